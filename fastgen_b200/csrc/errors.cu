@@ -1,0 +1,18 @@
+// Error message plumbing of the C interface.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void fg_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* fg_last_error() { return g_error; }
+
+extern "C" int fg_abi_version() { return 1; }

@@ -1,0 +1,268 @@
+"""Python face of the CUDA kernels: one :class:`Ops` per compute dtype.
+
+Every method launches hand-written kernels on the current CUDA stream through
+the C interface of the in-tree libraries.  The only library call is the bfloat16
+matrix product (cuBLAS through ``torch.mm``), where the reference calls
+``F.linear``; the float32 path uses this package's own float32 GEMM.  Nothing
+here falls back to the CPU or to eager PyTorch.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+FG_F32, FG_BF16 = 0, 1
+
+STATUS_BAD_PAGE = 1
+STATUS_BAD_TOKEN = 2
+STATUS_WAIT_TIMEOUT = 4
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return FG_F32
+    if dtype == torch.bfloat16:
+        return FG_BF16
+    raise TypeError(f"unsupported dtype {dtype}; the kernels take float32 and bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+_P, _I, _F = c_void_p, c_int, c_float
+
+_CORE_SIGNATURES = {
+    "fg_embedding": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fg_rmsnorm": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P],
+    "fg_silu_gate": [_P, _P, _I, _I, _I, _P],
+    "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
+    "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
+    "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
+}
+
+_ATTN_SIGNATURES = {
+    "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+}
+
+
+def _declare(lib: ctypes.CDLL, signatures) -> None:
+    lib.fg_last_error.restype = ctypes.c_char_p
+    for name, argtypes in signatures.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(lib: ctypes.CDLL, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.fg_last_error().decode())
+
+
+_core = None
+_attn = {}
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = build.core_library()
+        _declare(lib, _CORE_SIGNATURES)
+        _core = lib
+    return _core
+
+
+def attn(head_dim: int):
+    lib = _attn.get(head_dim)
+    if lib is None:
+        lib = build.attention_library(head_dim)
+        _declare(lib, _ATTN_SIGNATURES)
+        _attn[head_dim] = lib
+    return lib
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError(
+            f"fastgen_b200 runs on a CUDA device only (got {device}); there is no CPU path"
+        )
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; fastgen_b200 has no CPU path")
+    return device
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def attention_tiling(n_heads: int, n_kv_heads: int) -> int:
+    """Tokens per attention tile for a head grouping (see attention.cu)."""
+    group = n_heads // n_kv_heads
+    return max(1, 16 // min(group, 16))
+
+
+class Ops:
+    """Kernels bound to one compute dtype (``torch.float32`` or ``torch.bfloat16``).
+
+    ``act_dtype`` is the type of activations, weights' matrices and the cache;
+    the residual stream, norms' arithmetic, softmax and rotation angles are
+    float32 in both modes.
+    """
+
+    def __init__(self, dtype: torch.dtype, device) -> None:
+        self.device = require_cuda(device)
+        self.act_dtype = dtype
+        self.code = _code(dtype)
+        self.lib = core()
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # -- status word ---------------------------------------------------------
+    def check_status(self) -> None:
+        """Read the device status word (synchronises) and raise if a kernel
+        recorded a fault instead of performing a bad access."""
+        word = int(self.status.item())
+        if word:
+            self.status.zero_()
+            faults = []
+            if word & STATUS_BAD_PAGE:
+                faults.append("a block-table entry was missing or out of range")
+            if word & STATUS_BAD_TOKEN:
+                faults.append("a token id was outside the vocabulary")
+            if word & STATUS_WAIT_TIMEOUT:
+                faults.append("a bounded wait inside a kernel gave up")
+            raise KernelError("kernel status: " + "; ".join(faults))
+
+    # -- kernels ---------------------------------------------------------------
+    def embedding(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        assert table.is_contiguous() and out.is_contiguous() and tokens.dtype == torch.int32
+        n, dim = out.shape
+        _check(self.lib, self.lib.fg_embedding(
+            _ptr(table), _code(table.dtype), _ptr(tokens), _ptr(out), _code(out.dtype),
+            n, dim, table.shape[0], _ptr(self.status), _stream()))
+        return out
+
+    def rmsnorm(self, h, weight, eps: float, out=None, delta=None, rows=None):
+        """``h += delta`` (if given), then ``out = rmsnorm(h) * weight``.
+        With ``out=None`` and a delta only the sum is done.  With ``rows``
+        (int32 indices) only those rows are summed and normed into ``out``
+        [len(rows), dim] and ``h`` is left as it was."""
+        assert h.is_contiguous() and weight.is_contiguous()
+        dim = h.shape[1]
+        n = h.shape[0] if rows is None else rows.numel()
+        if delta is not None:
+            assert delta.is_contiguous() and delta.shape == h.shape
+        if out is not None:
+            assert out.is_contiguous() and out.shape == (n, dim)
+        if rows is not None:
+            assert rows.dtype == torch.int32 and out is not None
+        _check(self.lib, self.lib.fg_rmsnorm(
+            _ptr(h), _code(h.dtype), _ptr(delta), _code(delta.dtype) if delta is not None else 0,
+            _ptr(weight), _code(weight.dtype), _ptr(out), _code(out.dtype) if out is not None else 0,
+            _ptr(rows), n, dim, float(eps), _stream()))
+        return out
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``x @ w.T`` for ``x`` [M, K] and ``w`` [N, K] (fastgen/forward.py:438-440)."""
+        m, k = x.shape
+        n = w.shape[0]
+        assert w.shape[1] == k and x.stride(1) == 1 and w.stride(1) == 1
+        if self.act_dtype == torch.float32:
+            assert x.dtype == torch.float32 and w.dtype == torch.float32
+            if out is None:
+                out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+            assert out.dtype == torch.float32 and out.stride(1) == 1
+            _check(self.lib, self.lib.fg_gemm_f32_nt(
+                _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0),
+                m, n, k, _stream()))
+            return out
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        want = out.dtype if out is not None else (out_dtype or torch.bfloat16)
+        if want == torch.bfloat16:
+            return torch.mm(x, w.t(), out=out) if out is not None else torch.mm(x, w.t())
+        # float32 result of a bfloat16 product (logits)
+        res = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    def silu_gate(self, x13: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        n, two_f = x13.shape
+        assert x13.is_contiguous() and out.is_contiguous() and out.shape == (n, two_f // 2)
+        _check(self.lib, self.lib.fg_silu_gate(_ptr(x13), _ptr(out), _code(x13.dtype), n, two_f // 2, _stream()))
+        return out
+
+    def rope_kv_write(self, q, k, v, pos, req, freqs, k_pages, v_pages, block_table,
+                      page_size: int, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        """Rotate ``q`` in place; rotate ``k`` and copy ``v`` into their pages.
+        ``q``/``k``/``v`` are row-strided views [T, heads*head_dim]; ``k``/``v``
+        may both be ``None`` (queries only)."""
+        t = q.shape[0]
+        assert q.stride(1) == 1 and pos.dtype == torch.int32 and req.dtype == torch.int32
+        if k is not None:
+            assert k.stride(1) == 1 and v.stride(1) == 1
+            assert k_pages.is_contiguous() and v_pages.is_contiguous()
+            assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+            n_pages = k_pages.shape[0]
+            width = block_table.shape[1]
+        else:
+            n_pages = width = 0
+        _check(self.lib, self.lib.fg_rope_kv_write(
+            _ptr(q), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0,
+            _ptr(v), v.stride(0) if v is not None else 0, _code(q.dtype), _ptr(pos), _ptr(req),
+            _ptr(freqs), _ptr(k_pages) if k is not None else None,
+            _ptr(v_pages) if k is not None else None,
+            _ptr(block_table) if k is not None else None, width, page_size, n_pages,
+            t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
+
+    def attention(self, q, out, k_pages, v_pages, block_table, page_size: int, pos,
+                  tiles, n_heads: int, n_kv_heads: int, head_dim: int,
+                  window: Optional[int], scale: float) -> None:
+        """Paged causal attention of the step's query tokens.  ``tiles`` is the
+        step's :class:`AttentionTiles` for this head grouping."""
+        lib = attn(head_dim)
+        assert q.stride(1) == 1 and out.stride(1) == 1
+        _check(lib, lib.fg_attention_simt(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), _ptr(k_pages),
+            _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size, k_pages.shape[0],
+            _ptr(pos), _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
+            n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+            _ptr(self.status), _stream()))
+
+    def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
+               out_tokens, out_logprobs=None, scratch=None) -> torch.Tensor:
+        rows, vocab = logits.shape
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1
+        assert out_tokens.dtype == torch.int32
+        if temps is not None:
+            assert temps.dtype == torch.float32 and scratch is not None
+            assert scratch.numel() >= rows * vocab and scratch.dtype == torch.float32
+        if req_keys is not None:
+            assert req_keys.dtype == torch.int64 and positions.dtype == torch.int32
+        _check(self.lib, self.lib.fg_sample(
+            _ptr(logits), logits.stride(0), rows, vocab, _ptr(temps), float(top_p),
+            int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(req_keys), _ptr(positions), _ptr(out_tokens),
+            _ptr(out_logprobs), _ptr(scratch), _stream()))
+        return out_tokens
+
+    def sample_uniform(self, seed: int, req_keys, positions) -> torch.Tensor:
+        n = req_keys.numel()
+        out = torch.empty(n, dtype=torch.float32, device=self.device)
+        _check(self.lib, self.lib.fg_sample_uniform(
+            int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(req_keys), _ptr(positions), _ptr(out), n, _stream()))
+        return out

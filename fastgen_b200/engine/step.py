@@ -1,0 +1,221 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+The reference has two entry points, ``prefill`` for prompt portions given as
+``(n0, n1)`` pairs and a graph-captured ``decode`` (fastgen/forward.py:518-606);
+a decoded token is just the pair ``(len-1, 1)``.  Here there is one ``step``: a
+batch may hold portions of prompts beside single decoded tokens, cut anywhere.
+It runs only the tokens it is given, reads everything earlier from the cache,
+writes the new keys and values, and returns float32 logits at the wanted places
+only.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, OutOfPages, RequestCache
+from ..csrc.ops import attention_tiling
+from .model import Model
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens and the places among them whose logits are wanted."""
+
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class AttentionTiles:
+    """Device arrays that cut the step's tokens into attention tiles."""
+
+    req: torch.Tensor
+    tok0: torch.Tensor
+    ntok: torch.Tensor
+    n: int
+
+
+class StepContext:
+    """Everything about the step's batch that parts may need, on host and device.
+
+    Per token (device int32 ``[T]``): ``tokens``, ``pos`` (position in its
+    request), ``req`` (its request's slot: the row of the block tables and the
+    index of the fixed-size state; negative = padding).
+    Per sequence of the batch (host lists and device int32): ``seq_slot``,
+    ``seq_start`` (first token index, ``[B+1]``), ``seq_cached`` (tokens already
+    in the cache before this step).
+    """
+
+    def __init__(self, device) -> None:
+        self.device = device
+        self.n_tokens = 0
+        self.n_seqs = 0
+        self.n_want = 0
+        self.tokens = self.pos = self.req = self.want_rows = None
+        self.seq_slot = self.seq_start = self.seq_cached = None
+        self.host_seq_slot: List[int] = []
+        self.host_seq_start: List[int] = [0]
+        self.host_seq_cached: List[int] = []
+        self._tiles: Dict[int, AttentionTiles] = {}
+
+    def attention_tiles(self, n_heads: int, n_kv_heads: int) -> AttentionTiles:
+        tpt = attention_tiling(n_heads, n_kv_heads)
+        tiles = self._tiles.get(tpt)
+        if tiles is None:
+            tiles = self._build_tiles(tpt)
+            self._tiles[tpt] = tiles
+        return tiles
+
+    def _build_tiles(self, tpt: int) -> AttentionTiles:
+        req, tok0, ntok = [], [], []
+        for b, slot in enumerate(self.host_seq_slot):
+            start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
+            for t in range(start, end, tpt):
+                req.append(slot)
+                tok0.append(t)
+                ntok.append(min(tpt, end - t))
+        n = len(req)
+        packed = torch.tensor(req + tok0 + ntok, dtype=torch.int32).to(self.device)
+        return AttentionTiles(packed[:n], packed[n : 2 * n], packed[2 * n :], n)
+
+
+class Engine:
+    """A model, its cache and the step function over them."""
+
+    def __init__(
+        self,
+        model: Model,
+        page_size: int,
+        n_pages: int,
+        max_requests: int,
+        max_length: Optional[int] = None,
+    ) -> None:
+        self.model = model
+        self.ops = model.ops
+        self.device = model.ops.device
+        args = model.args
+        if max_length is None:
+            max_length = args.max_positions
+        max_length = min(max_length, args.max_positions)
+        self.max_length = max_length
+        self.cache = CacheManager(
+            model.cache_specs(),
+            model.state_specs(),
+            model.kv_from(),
+            page_size=page_size,
+            n_pages=n_pages,
+            max_requests=max_requests,
+            max_length=max_length,
+            dtype=model.ops.act_dtype,
+            device=self.device,
+        )
+        self.memories = [self.cache.memory(e) for e in range(len(args.schedule))]
+
+    # -- requests --------------------------------------------------------------
+    def admit(self, request_id) -> RequestCache:
+        return self.cache.admit(request_id)
+
+    def release(self, request_id) -> None:
+        self.cache.release(request_id)
+
+    def length(self, request_id) -> int:
+        return self.cache.get(request_id).length
+
+    # -- the step --------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
+        vocab = self.model.args.vocab_size
+        seen = set()
+        reqs = []
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            req = self.cache.get(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            for tok in e.tokens:
+                if not 0 <= int(tok) < vocab:
+                    raise ValueError(
+                        f"token id {tok} of request {e.request_id!r} is outside the vocabulary of {vocab}"
+                    )
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(
+                        f"request {e.request_id!r} wants logits at place {w} of {n} tokens"
+                    )
+            if req.length + n > self.max_length:
+                raise OutOfPages(
+                    f"request {e.request_id!r} would reach {req.length + n} tokens, more than "
+                    f"the {self.max_length} positions this engine was built for"
+                )
+            reqs.append(req)
+        return reqs
+
+    def build_context(self, entries: Sequence[StepEntry], reqs: Sequence[RequestCache]) -> StepContext:
+        ctx = StepContext(self.device)
+        tokens, pos, rq, want = [], [], [], []
+        for e, req in zip(entries, reqs):
+            n = len(e.tokens)
+            base = len(tokens)
+            tokens.extend(int(t) for t in e.tokens)
+            pos.extend(range(req.length, req.length + n))
+            rq.extend([req.slot] * n)
+            want.extend(base + int(w) for w in e.want)
+            ctx.host_seq_slot.append(req.slot)
+            ctx.host_seq_cached.append(req.length)
+            ctx.host_seq_start.append(base + n)
+        t, b, nw = len(tokens), len(entries), len(want)
+        packed = np.concatenate(
+            [
+                np.asarray(tokens, dtype=np.int32),
+                np.asarray(pos, dtype=np.int32),
+                np.asarray(rq, dtype=np.int32),
+                np.asarray(want, dtype=np.int32),
+                np.asarray(ctx.host_seq_slot, dtype=np.int32),
+                np.asarray(ctx.host_seq_start, dtype=np.int32),
+                np.asarray(ctx.host_seq_cached, dtype=np.int32),
+            ]
+        )
+        dev = torch.from_numpy(packed).to(self.device)
+        o = 0
+        ctx.tokens, o = dev[o : o + t], o + t
+        ctx.pos, o = dev[o : o + t], o + t
+        ctx.req, o = dev[o : o + t], o + t
+        ctx.want_rows, o = dev[o : o + nw], o + nw
+        ctx.seq_slot, o = dev[o : o + b], o + b
+        ctx.seq_start, o = dev[o : o + b + 1], o + b + 1
+        ctx.seq_cached, o = dev[o : o + b], o + b
+        ctx.n_tokens, ctx.n_seqs, ctx.n_want = t, b, nw
+        return ctx
+
+    @torch.inference_mode()
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits ``[wanted, vocab]`` in the order
+        of the entries and of their ``want`` lists, or ``None`` if nothing is
+        wanted.  Raises :class:`OutOfPages` (before touching anything on the
+        device) when the cache cannot take the new tokens."""
+        if not entries:
+            return None
+        reqs = self._validate(entries)
+        need = [0] * len(self.cache.groups)
+        for e, req in zip(entries, reqs):
+            for g, n in enumerate(self.cache.pages_needed(req, req.length + len(e.tokens))):
+                need[g] += n
+        free = self.cache.free_pages()
+        if any(n > f for n, f in zip(need, free)):
+            raise OutOfPages(f"the step needs {need} new pages per group, free: {free}")
+        for e, req in zip(entries, reqs):
+            self.cache.reserve(req, req.length + len(e.tokens))
+        self.cache.flush_tables()
+        ctx = self.build_context(entries, reqs)
+        logits = self.model.forward(ctx, self.memories)
+        for e, req in zip(entries, reqs):
+            self.cache.advance(req, req.length + len(e.tokens))
+        return logits

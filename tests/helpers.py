@@ -1,0 +1,214 @@
+"""Shared test fixtures: tiny configurations, model folders, replay plans."""
+
+from __future__ import annotations
+
+import json
+import random
+from pathlib import Path
+from typing import Dict, List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+import plain_llama as pl
+from fastgen_b200.weights import write_random_model
+
+# Three tiny Llama configurations that differ in every size and option.
+TINY_A = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=176,
+    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
+    rms_norm_eps=1e-5, vocab_size=256, tie_word_embeddings=True, rope_theta=10000.0,
+    max_position_embeddings=256,
+)
+TINY_B = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=192, intermediate_size=512,
+    num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=3,
+    rms_norm_eps=1e-6, vocab_size=320, tie_word_embeddings=False, rope_theta=500000.0,
+    rope_scaling=dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=64, rope_type="llama3"),
+    max_position_embeddings=512,
+)
+# odd sizes: width and vocabulary no power of two, head size 48 given explicitly,
+# group of 3, a window
+TINY_C = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=200, intermediate_size=328,
+    num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=48,
+    rms_norm_eps=1e-5, vocab_size=331, tie_word_embeddings=False, rope_theta=10000.0,
+    rope_scaling=dict(factor=4.0, low_freq_factor=1.0, high_freq_factor=2.0,
+                      original_max_position_embeddings=32),
+    sliding_window=24, max_position_embeddings=384,
+)
+CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 2), "tiny_c": (TINY_C, 7)}
+
+
+def make_model_dir(tmp_path, name: str, std: float = None) -> Path:
+    cfg, seed = CONFIGS[name]
+    return write_random_model(Path(tmp_path) / name, cfg, seed, dtype=torch.bfloat16,
+                              norm_jitter=0.1, std=std)
+
+
+def random_tokens(vocab: int, n: int, seed: int) -> List[int]:
+    rng = random.Random(seed)
+    return [rng.randrange(vocab) for _ in range(n)]
+
+
+_plain_cache: Dict[Tuple[str, Tuple[int, ...]], np.ndarray] = {}
+
+
+def plain_logits(model_dir, tokens: Sequence[int]) -> np.ndarray:
+    """Logits [T, vocab] of the plain implementation (float64 arithmetic)."""
+    key = (str(model_dir), tuple(tokens))
+    if key not in _plain_cache:
+        model = pl.read_model(model_dir, torch.float64)
+        _plain_cache[key] = pl.forward(model, list(tokens)).numpy()
+    return _plain_cache[key]
+
+
+# ---------------------------------------------------------------------------
+# replay plans: lists of steps in the trace format
+# ---------------------------------------------------------------------------
+def plan_whole(requests: Dict[str, List[int]]):
+    steps = []
+    for i, (rid, toks) in enumerate(requests.items()):
+        steps.append(dict(step=i, entries=[dict(id=rid, tokens=toks, want=list(range(len(toks))))],
+                          end=[rid]))
+    return steps
+
+
+def plan_decode_tail(requests: Dict[str, List[int]], tail: int = 32):
+    steps, n = [], 0
+    for rid, toks in requests.items():
+        head = max(1, len(toks) - tail)
+        steps.append(dict(step=n, entries=[dict(id=rid, tokens=toks[:head], want=list(range(head)))], end=[]))
+        n += 1
+        for p in range(head, len(toks)):
+            steps.append(dict(step=n, entries=[dict(id=rid, tokens=[toks[p]], want=[0])],
+                              end=[rid] if p == len(toks) - 1 else []))
+            n += 1
+        if head == len(toks):
+            steps[-1]["end"] = [rid]
+    return steps
+
+
+def plan_portions(requests: Dict[str, List[int]], sizes=(2, 3, 5, 7, 2, 11, 4, 13, 2, 17)):
+    steps, n = [], 0
+    for rid, toks in requests.items():
+        p, k = 0, 0
+        while p < len(toks):
+            m = min(sizes[k % len(sizes)], len(toks) - p)
+            steps.append(dict(step=n, entries=[dict(id=rid, tokens=toks[p:p + m], want=list(range(m)))],
+                              end=[rid] if p + m == len(toks) else []))
+            n += 1
+            p += m
+            k += 1
+    return steps
+
+
+def plan_mixed(requests: Dict[str, List[int]], seed: int, max_live: int = 4, prompt_frac: float = 0.6):
+    """Up to ``max_live`` requests at a time: prompt portions of some beside single
+    decoded tokens of others; a finished request's pages go to the next one."""
+    rng = random.Random(seed)
+    waiting = list(requests.items())
+    live: Dict[str, Dict] = {}
+    steps, n = [], 0
+    while waiting or live:
+        while waiting and len(live) < max_live and (not live or rng.random() < 0.7):
+            rid, toks = waiting.pop(0)
+            live[rid] = dict(toks=toks, p=0, prompt=max(1, int(len(toks) * prompt_frac)))
+        entries, end = [], []
+        for rid, st in list(live.items()):
+            if len(live) > 1 and rng.random() < 0.15:
+                continue  # this request sits the step out
+            if st["p"] < st["prompt"]:
+                m = min(rng.choice([2, 3, 5, 8, 16, 21]), st["prompt"] - st["p"])
+            else:
+                m = 1
+            toks = st["toks"][st["p"]:st["p"] + m]
+            entries.append(dict(id=rid, tokens=toks, want=list(range(m))))
+            st["p"] += m
+            if st["p"] == len(st["toks"]):
+                end.append(rid)
+                del live[rid]
+        if entries:
+            steps.append(dict(step=n, entries=entries, end=end))
+            n += 1
+    return steps
+
+
+def max_live_tokens(steps, page: int = 64) -> int:
+    """The most tokens live requests hold at any time, each rounded up to ``page``."""
+    held: Dict[str, int] = {}
+    worst = 0
+    for st in steps:
+        for e in st["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        worst = max(worst, sum(-(-v // page) * page for v in held.values()))
+        for rid in st["end"]:
+            held.pop(rid, None)
+    return worst
+
+
+def collect(steps, outputs: Dict[int, np.ndarray]) -> Dict[str, Dict[int, np.ndarray]]:
+    """Map step outputs back to (request, position) -> logits row."""
+    pos: Dict[str, int] = {}
+    got: Dict[str, Dict[int, np.ndarray]] = {}
+    for st in steps:
+        row = 0
+        for e in st["entries"]:
+            base = pos.get(e["id"], 0)
+            for w in e["want"]:
+                got.setdefault(e["id"], {})[base + w] = outputs[st["step"]][row]
+                row += 1
+            pos[e["id"]] = base + len(e["tokens"])
+        for rid in st["end"]:
+            pos.pop(rid, None)
+    return got
+
+
+def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_requests: int = 4):
+    """Replay ``steps`` through the package's engine in this process."""
+    from fastgen_b200.engine import Engine, Model, StepEntry
+
+    model = Model.load(model_dir, dtype, "cuda:0")
+    n_pages = max(1, -(-max_tokens // page_size))
+    engine = Engine(model, page_size=page_size, n_pages=n_pages, max_requests=max_requests,
+                    max_length=min(model.args.max_positions, n_pages * page_size))
+    outputs, live = {}, set()
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            if e["id"] not in live:
+                engine.admit(e["id"])
+                live.add(e["id"])
+            entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
+        logits = engine.step(entries)
+        if logits is not None:
+            outputs[st["step"]] = logits.float().cpu().numpy()
+        engine.ops.check_status()
+        for rid in st["end"]:
+            engine.release(rid)
+            live.discard(rid)
+        engine.cache.check()
+    return outputs, engine
+
+
+def compare(model_dir, requests, got, dtype) -> float:
+    """Compare every collected row with the plain implementation; return the
+    largest absolute error.  float32 must agree to 1e-4 with the same argmax;
+    bfloat16 within 2% of the logits' range (see tolerance notes in the tests)."""
+    worst = 0.0
+    for rid, toks in requests.items():
+        ref = plain_logits(model_dir, toks)
+        assert set(got[rid]) == set(range(len(toks))), f"{rid}: positions missing"
+        for p, row in got[rid].items():
+            err = float(np.abs(row - ref[p]).max())
+            worst = max(worst, err)
+            if dtype == torch.float32:
+                assert err <= 1e-4, f"{rid} pos {p}: max abs err {err:.3e}"
+                top = np.sort(ref[p])[-2:]
+                if top[1] - top[0] > 2e-4:
+                    assert int(row.argmax()) == int(ref[p].argmax()), f"{rid} pos {p}: argmax differs"
+            else:
+                scale = float(np.abs(ref[p]).max())
+                assert err <= 0.02 * max(scale, 1.0), f"{rid} pos {p}: err {err:.3e} vs scale {scale:.3e}"
+    return worst

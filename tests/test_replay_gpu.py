@@ -1,0 +1,74 @@
+"""Replay through the engine, compared with the plain implementation."""
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+PAGES = {"tiny_a": 8, "tiny_b": 16, "tiny_c": 8}
+
+
+def _requests(name, lengths, seed):
+    vocab = H.CONFIGS[name][0]["vocab_size"]
+    return {f"r{i}": H.random_tokens(vocab, n, seed + i) for i, n in enumerate(lengths)}
+
+
+LENGTHS = {"tiny_a": [7, 13, 1, 30, 70], "tiny_b": [1, 9, 40, 64, 100], "tiny_c": [5, 33, 90, 64]}
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(H.CONFIGS))
+@pytest.mark.parametrize("plan", ["whole", "tail", "portions", "mixed"])
+def test_replay(tmp_path, name, dtype, plan):
+    model_dir = H.make_model_dir(tmp_path, name)
+    reqs = _requests(name, LENGTHS[name], 100)
+    page = PAGES[name]
+    if plan == "whole":
+        steps = H.plan_whole(reqs)
+    elif plan == "tail":
+        steps = H.plan_decode_tail(reqs)
+    elif plan == "portions":
+        steps = H.plan_portions(reqs)
+    else:
+        reqs = _requests(name, LENGTHS[name] + [48, 17, 80], 200)
+        steps = H.plan_mixed(reqs, seed=5)
+    # exactly as many pages as the trace needs at its fullest: pages are reused
+    max_tokens = H.max_live_tokens(steps, page)
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page, max_tokens)
+    got = H.collect(steps, outputs)
+    H.compare(model_dir, reqs, got, dtype)
+    assert engine.cache.n_live == 0
+    assert all(f == g.pool.n_pages for f, g in zip(engine.cache.free_pages(), engine.cache.groups))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """The same through bin/trace_run, as a user runs it."""
+    name = "tiny_b"
+    model_dir = H.make_model_dir(tmp_path, name)
+    reqs = _requests(name, [9, 40, 100, 64, 33], 300)
+    steps = H.plan_mixed(reqs, seed=11)
+    out = tmp_path / "out"
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run(
+        [sys.executable, str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+         "--out", str(out), "--max-tokens", str(H.max_live_tokens(steps, 64))],
+        input="".join(json.dumps(s) + "\n" for s in steps), text=True, capture_output=True, timeout=900,
+    )
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
+    assert done == [f"done {s['step']}" for s in steps]
+    vocab = H.CONFIGS[name][0]["vocab_size"]
+    outputs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
+    got = H.collect(steps, outputs)
+    H.compare(model_dir, reqs, got, torch.float32 if dtype == "float32" else torch.bfloat16)
