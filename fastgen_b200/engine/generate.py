@@ -1,0 +1,233 @@
+"""The generator: the package's Python entry point, in the reference's manner.
+
+    fg = Fastgen.build(HfLoader(model_dir), GenArgs(...), tp_mesh=None,
+                       device=torch.device("cuda:0"))
+    q = queue.Queue()
+    q.put(Packet(thread_id=0, tokens=[...], temperature=0.8, max_gen=24))
+    q.put(None)
+    for pkt in fg.generate(q):
+        ...
+    fg.destroy()
+
+Names and meanings of ``GenArgs``, ``Packet``, ``Fastgen.build/generate/destroy``
+follow fastgen/generate.py:30-76, 139-173, 405-425.  Options of the reference
+that belong to features outside this engine (host cache, fp8, tensor
+parallelism) are not present; ``tp_mesh`` must be ``None``.
+"""
+
+from __future__ import annotations
+
+import logging
+import queue
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Generator, List, Optional, Union
+
+import torch
+
+from ..config import load_model_args, read_config
+from ..sampling import Sampler
+from .model import Model
+from .scheduler import Request, Scheduler
+from .step import Engine, StepEntry
+from .tune import mem_params
+
+logger = logging.getLogger("fastgen_b200")
+
+
+@dataclass
+class GenArgs:
+    use_sampling: bool = True
+    temperature: float = 0.7
+    top_p: float = 0.9
+    logprobs: bool = False
+
+    max_batch: int = 256
+    max_seq: int = -1  # total cache tokens; negative: from the memory budget
+    max_gen: Optional[int] = None
+
+    cache_block: int = 64  # tokens per cache page
+    num_cuda_graphs: int = 16
+
+    max_prefill: int = 8192  # tokens per step, prompt portions and decoded tokens together
+    prefill_gb: float = 0.5  # used by the memory budget
+    gpu_gb: float = 20  # ditto
+
+    sync_freq: int = 10
+    seed: int = 777
+
+
+@dataclass
+class Packet:
+    thread_id: Any
+    "An arbitrary identifier to link inputs to outputs."
+    tokens: List[int] = field(default_factory=list)
+    "The prompt if used as input, or else the generation output."
+    temperature: Optional[float] = None
+    "An optional per-generation temperature setting."
+    logprobs: Optional[List[float]] = None
+    "Logprobs of the output tokens; only when ``GenArgs.logprobs`` is set."
+    max_gen: Optional[int] = None
+    "The maximum number of tokens to generate."
+    error: Optional[str] = None
+    "Set on an output packet whose request could not be served."
+
+
+class HfLoader:
+    """A model folder: ``config.json``, safetensors and (optionally) a tokenizer."""
+
+    def __init__(self, model: Union[str, Path]) -> None:
+        self.directory = Path(model)
+        read_config(self.directory)  # fails early with a clear error
+
+    def load_model_args(self):
+        return load_model_args(self.directory)
+
+    def load_tokenizer(self):
+        from ..utils.tokenizer import HfTokenizer
+
+        return HfTokenizer(self.directory)
+
+    def has_tokenizer(self) -> bool:
+        return (self.directory / "tokenizer.json").is_file()
+
+    def load(self, dtype: torch.dtype, device) -> Model:
+        return Model.load(self.directory, dtype, device)
+
+
+class Fastgen:
+    @staticmethod
+    def build(loader: HfLoader, gen_args: GenArgs, tp_mesh=None,
+              device: Union[str, torch.device] = "cuda:0",
+              dtype: torch.dtype = torch.bfloat16) -> "Fastgen":
+        if tp_mesh is not None:
+            raise ValueError("this engine runs on one GPU; tp_mesh must be None")
+        device = torch.device(device)
+        t0 = time.monotonic()
+        model = loader.load(dtype, device)
+        logger.info("Built and loaded model in %.2fs", time.monotonic() - t0)
+        stop_tokens = list(model.args.stop_tokens)
+        if loader.has_tokenizer():
+            stop_tokens = loader.load_tokenizer().stop_tokens or stop_tokens
+        return Fastgen(gen_args, model, stop_tokens)
+
+    def __init__(self, args: GenArgs, model: Model, stop_tokens) -> None:
+        self.gen_args = args
+        self.model = model
+        self.ops = model.ops
+        self.device = model.ops.device
+        self.stop_tokens = list(stop_tokens)
+        self.generating = False
+        block = args.cache_block
+        act_bytes = 4 if model.ops.act_dtype == torch.float32 else 2
+
+        # pages: from max_seq, or from the memory budget (generate.py:206-236)
+        per_token = model.cache_bytes_per_token(act_bytes)
+        widest = max((getattr(l.ffn.params, "ffn_dim", model.args.dim) for l in model.args.layers))
+        mp = mem_params(model.weight_bytes(), per_token, model.args.dim, widest, act_bytes,
+                        max(args.prefill_gb, 0.1), args.gpu_gb)
+        mp.round_to(block)
+        max_seq = args.max_seq
+        if max_seq < 0:
+            max_seq = mp.cache_tokens
+            logger.info("Setting max sequence length to %d", max_seq)
+        max_seq = -(-max_seq // block) * block
+        if max_seq < block:
+            raise RuntimeError("Not enough memory available for the generation caches")
+        self.max_seq = max_seq
+        self.max_prefill = args.max_prefill if args.max_prefill > 0 else mp.prefill_tokens
+        self.max_batch = min(args.max_batch, max_seq // block)
+
+        self.engine = Engine(
+            model, page_size=block, n_pages=max_seq // block, max_requests=self.max_batch,
+            max_length=min(model.args.max_positions, max_seq),
+        )
+        self.sampler = Sampler(
+            self.ops, model.args.vocab_size, self.max_batch, use_sampling=args.use_sampling,
+            top_p=args.top_p, seed=args.seed, logprobs=args.logprobs,
+        )
+        self.scheduler = Scheduler(
+            self.engine.cache, self.max_batch, self.max_prefill, self.stop_tokens, args.max_gen
+        )
+        self.steps = 0
+
+    def destroy(self) -> None:
+        """Free what the generator holds on the device."""
+        self.engine = None
+        self.scheduler = None
+        self.sampler = None
+
+    # -- the loop ----------------------------------------------------------------
+    def _packet(self, req: Request) -> Packet:
+        return Packet(
+            thread_id=req.thread_id,
+            tokens=list(req.generated),
+            temperature=req.temperature,
+            logprobs=list(req.logprobs) if self.gen_args.logprobs else None,
+            max_gen=req.max_gen,
+            error=req.error,
+        )
+
+    def _pull(self, q: "queue.Queue[Optional[Packet]]", eoq: bool) -> bool:
+        """Move packets from the queue to the scheduler; block only when idle."""
+        while not eoq:
+            try:
+                pkt = q.get(block=not self.scheduler.has_work())
+            except queue.Empty:
+                break
+            if pkt is None:
+                return True
+            # generate.py:790: a per-request temperature of 0 falls back to the default
+            temp = pkt.temperature or self.gen_args.temperature
+            if not self.gen_args.use_sampling:
+                temp = 0.0
+            self.scheduler.add(pkt.thread_id, pkt.tokens, temp, pkt.max_gen)
+            if len(self.scheduler.waiting) >= 2 * self.max_batch:
+                break
+        return eoq
+
+    def generate(self, q: "queue.Queue[Optional[Packet]]") -> Generator[Packet, None, None]:
+        """Read prompts from the queue and yield a completion (or an error) for
+        each; outputs may come in another order than inputs.  ``None`` in the
+        queue ends the input; what is in flight is completed."""
+        assert not self.generating, "multiple generators cannot run concurrently"
+        self.generating = True
+        try:
+            yield from self._generate(q)
+        finally:
+            self.generating = False
+
+    @torch.inference_mode()
+    def _generate(self, q):
+        sched = self.scheduler
+        eoq = False
+        while not eoq or sched.has_work() or sched.finished:
+            eoq = self._pull(q, eoq)
+            for req in sched.take_finished():
+                yield self._packet(req)
+            plan = sched.plan()
+            if not plan:
+                if sched.has_work():
+                    raise RuntimeError("the scheduler made no progress")  # cannot happen: see Scheduler.add
+                continue
+            entries = [
+                StepEntry(id(e.request), e.tokens, [len(e.tokens) - 1] if e.samples else [])
+                for e in plan
+            ]
+            logits = self.engine.step_reserved(entries)
+            self.steps += 1
+            sampling = [e for e in plan if e.samples]
+            tokens: List[int] = []
+            logprobs = None
+            if sampling:
+                out, lp = self.sampler.sample(
+                    logits,
+                    [e.request.temperature for e in sampling],
+                    [e.request.key for e in sampling],
+                    [len(e.request) for e in sampling],
+                )
+                tokens = out.tolist()  # the step's one device-to-host read
+                logprobs = lp.tolist() if lp is not None else None
+            for req in sched.commit(plan, tokens, logprobs):
+                yield self._packet(req)

@@ -93,6 +93,14 @@ class Model:
     def kv_from(self) -> List[Optional[int]]:
         return [e.kv_from for e in self.args.schedule]
 
+    def cache_bytes_per_token(self, elt_size: int) -> int:
+        """Bytes of keys and values one token adds over all runs that own a cache."""
+        total = 0
+        for spec, src in zip(self.cache_specs(), self.kv_from()):
+            if spec is not None and src is None:
+                total += 2 * spec.n_kv_heads * spec.head_dim * elt_size
+        return total
+
     def weight_bytes(self) -> int:
         """Bytes of every tensor a step reads (fused buffers, embedding once if tied)."""
         seen, total = set(), 0

@@ -213,9 +213,21 @@ class Engine:
             raise OutOfPages(f"the step needs {need} new pages per group, free: {free}")
         for e, req in zip(entries, reqs):
             self.cache.reserve(req, req.length + len(e.tokens))
-        self.cache.flush_tables()
-        ctx = self.build_context(entries, reqs)
-        logits = self.model.forward(ctx, self.memories)
+        logits = self._run(entries, reqs)
         for e, req in zip(entries, reqs):
             self.cache.advance(req, req.length + len(e.tokens))
         return logits
+
+    @torch.inference_mode()
+    def step_reserved(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """The step for a caller that manages the cache itself (the scheduler):
+        pages for the new tokens are already reserved and the caller records the
+        new lengths afterwards."""
+        if not entries:
+            return None
+        return self._run(entries, self._validate(entries))
+
+    def _run(self, entries, reqs) -> Optional[torch.Tensor]:
+        self.cache.flush_tables()
+        ctx = self.build_context(entries, reqs)
+        return self.model.forward(ctx, self.memories)

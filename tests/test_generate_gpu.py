@@ -1,0 +1,134 @@
+"""Generation through the Python entry point and the command line."""
+
+import queue
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+
+
+def _generate(model_dir, prompts, dtype, **kw):
+    from fastgen_b200.engine import Fastgen, GenArgs, HfLoader, Packet
+
+    args = GenArgs(**kw)
+    fg = Fastgen.build(HfLoader(model_dir), args, tp_mesh=None, device=torch.device("cuda:0"), dtype=dtype)
+    q = queue.Queue()
+    for i, p in enumerate(prompts):
+        q.put(Packet(thread_id=i, tokens=p))
+    q.put(None)
+    out = {pkt.thread_id: pkt for pkt in fg.generate(q)}
+    stats = dict(preemptions=fg.scheduler.n_preemptions, steps=fg.steps)
+    fg.engine.cache.check()
+    assert fg.engine.cache.n_live == 0
+    fg.destroy()
+    return out, stats
+
+
+def test_greedy_generation_equals_plain(tmp_path):
+    """tiny-A workload: prompts 7, 13, 1, 30; 16 greedy tokens; pages of 8 (float32)."""
+    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    prompts = [H.random_tokens(256, n, 1 + i) for i, n in enumerate([7, 13, 1, 30])]
+    out, _ = _generate(model_dir, prompts, torch.float32, use_sampling=False, max_gen=16,
+                       cache_block=8, max_seq=256, max_batch=4, max_prefill=16)
+    model = pl.read_model(model_dir)
+    for i, p in enumerate(prompts):
+        assert out[i].tokens == pl.greedy(model, p, 16), f"prompt {i}"
+
+
+def test_greedy_with_preemption_equals_plain(tmp_path):
+    """So few pages that requests are preempted and recomputed; tokens do not change."""
+    model_dir = H.make_model_dir(tmp_path, "tiny_b")
+    prompts = [H.random_tokens(320, n, 10 + i) for i, n in enumerate([9, 40, 24, 17])]
+    out, stats = _generate(model_dir, prompts, torch.float32, use_sampling=False, max_gen=12,
+                           cache_block=16, max_seq=96, max_batch=4, max_prefill=16)
+    assert stats["preemptions"] >= 1
+    model = pl.read_model(model_dir)
+    for i, p in enumerate(prompts):
+        assert out[i].tokens == pl.greedy(model, p, 12), f"prompt {i}"
+
+
+def test_bf16_greedy_follows_plain_where_the_margin_is_clear(tmp_path):
+    model_dir = H.make_model_dir(tmp_path, "tiny_b", std=0.08)
+    prompts = [H.random_tokens(320, n, 20 + i) for i, n in enumerate([5, 33])]
+    out, _ = _generate(model_dir, prompts, torch.bfloat16, use_sampling=False, max_gen=8,
+                       cache_block=16, max_seq=256, max_batch=2)
+    model = pl.read_model(model_dir)
+    for i, p in enumerate(prompts):
+        seq = list(p)
+        for tok in out[i].tokens:
+            logits = pl.forward(model, seq)[-1].numpy()
+            # the engine's token is the plain argmax, or within bfloat16 error of it
+            assert logits[tok] >= logits.max() - 0.02 * max(1.0, np.abs(logits).max())
+            seq.append(tok)
+
+
+def test_sampling_is_seeded_and_independent_of_batching(tmp_path):
+    """tiny-B workload: temperature 0.8, seeded; prompts prefilled in portions of 16
+    beside decoding requests give the same tokens as each request alone."""
+    model_dir = H.make_model_dir(tmp_path, "tiny_b")
+    prompts = [H.random_tokens(320, n, 3 + i) for i, n in enumerate([1, 9, 40, 64, 100])]
+    kw = dict(use_sampling=True, temperature=0.8, top_p=0.9, max_gen=24, cache_block=16,
+              max_seq=512, seed=5, logprobs=True)
+    together, _ = _generate(model_dir, prompts, torch.float32, max_batch=4, max_prefill=16, **kw)
+    again, _ = _generate(model_dir, prompts, torch.float32, max_batch=4, max_prefill=16, **kw)
+    other, _ = _generate(model_dir, prompts, torch.float32, max_batch=4, max_prefill=16, **dict(kw, seed=6))
+    for i in range(len(prompts)):
+        assert together[i].tokens == again[i].tokens
+        assert len(together[i].tokens) == 24 and len(together[i].logprobs) == 24
+    assert any(together[i].tokens != other[i].tokens for i in range(len(prompts)))
+    # alone: same request keys are needed for the same draws, so run them in the same order, one lane
+    alone, _ = _generate(model_dir, prompts, torch.float32, max_batch=1, max_prefill=512, **kw)
+    same = sum(together[i].tokens == alone[i].tokens for i in range(len(prompts)))
+    assert same == len(prompts)
+    # logprobs are those of the plain implementation
+    model = pl.read_model(model_dir)
+    seq = prompts[1] + together[1].tokens
+    logits = pl.forward(model, seq[:-1])
+    lp = torch.log_softmax(logits.double(), -1)
+    for k, tok in enumerate(together[1].tokens):
+        assert abs(float(lp[len(prompts[1]) - 1 + k, tok]) - together[1].logprobs[k]) < 1e-3
+
+
+def test_stop_token_and_errors(tmp_path):
+    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    model = pl.read_model(model_dir)
+    prompt = H.random_tokens(256, 7, 1)
+    ref = pl.greedy(model, prompt, 16)
+    from fastgen_b200.engine import Fastgen, GenArgs, HfLoader, Packet
+
+    fg = Fastgen.build(HfLoader(model_dir), GenArgs(use_sampling=False, max_gen=16, cache_block=8, max_seq=64,
+                                                    max_batch=2), device="cuda:0", dtype=torch.float32)
+    fg.scheduler.stop_tokens = {ref[3]}
+    q = queue.Queue()
+    q.put(Packet(thread_id="stop", tokens=prompt))
+    q.put(Packet(thread_id="long", tokens=H.random_tokens(256, 80, 2)))
+    q.put(Packet(thread_id="capped", tokens=prompt, max_gen=2))
+    q.put(None)
+    out = {p.thread_id: p for p in fg.generate(q)}
+    first = ref.index(ref[3])
+    assert out["stop"].tokens == ref[: first + 1]
+    assert out["long"].error and out["long"].tokens == []
+    assert len(out["capped"].tokens) <= 2
+    fg.destroy()
+
+
+def test_fgchat_token_id_mode(tmp_path):
+    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run(
+        [sys.executable, str(root / "bin" / "fgchat"), str(model_dir), "--temperature", "0.0",
+         "--max-tokens", "6", "--dtype", "fp32", "--page-size", "8", "--max-seq", "128"],
+        input="5 17 3 200\n/q\n", text=True, capture_output=True, timeout=600,
+    )
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    ref = pl.greedy(pl.read_model(model_dir), [5, 17, 3, 200], 6)
+    assert " ".join(map(str, ref)) in proc.stdout
+    assert "--- [6 tokens," in proc.stdout
