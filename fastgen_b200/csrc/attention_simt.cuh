@@ -59,6 +59,15 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
   auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
 
+  if (b < 0) {
+    // padding of a fixed-size batch: no request, the output rows are zeroed
+    for (int i = tid; i < ROWS * HD; i += THREADS) {
+      const int r = i / HD, d = i - r * HD;
+      if (row_valid(r))
+        out[(size_t)(tok0 + row_token(r)) * out_stride + (g * group + row_head(r)) * HD + d] = from_f32<T>(0.f);
+    }
+    return;
+  }
   if (tid < ROWS) row_pos[tid] = row_valid(tid) ? pos[tok0 + row_token(tid)] : -1;
   for (int i = tid; i < ROWS * HD; i += THREADS) {
     const int r = i / HD, d = i - r * HD;

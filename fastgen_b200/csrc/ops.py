@@ -70,6 +70,7 @@ class KernelError(RuntimeError):
 def _check(lib: ctypes.CDLL, rc: int) -> None:
     if rc != 0:
         raise KernelError(lib.fg_last_error().decode())
+    Ops.launches += 1
 
 
 _core = None
@@ -122,6 +123,8 @@ class Ops:
     the residual stream, norms' arithmetic, softmax and rotation angles are
     float32 in both modes.
     """
+
+    launches = 0  # kernels of this package launched (graph replays add their kernels)
 
     def __init__(self, dtype: torch.dtype, device) -> None:
         self.device = require_cuda(device)

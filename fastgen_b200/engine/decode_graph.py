@@ -1,0 +1,97 @@
+"""CUDA graphs for steps in which every request brings exactly one token.
+
+The reference captures ``decode`` once per batch-size bucket at start-up and
+replays it with inputs copied into fixed tensors (fastgen/generate.py:300-347,
+685-718; fastgen/forward.py:95-151).  The same here, captured lazily: a bucket
+of size ``n`` owns fixed device buffers for the tokens, positions and slots of
+``n`` lanes; a step with fewer requests pads the rest with slot ``-1``, which
+every kernel treats as "no request" (nothing is written to any page).
+"""
+
+from __future__ import annotations
+
+import bisect
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc.ops import Ops
+from .step import AttentionTiles, StepContext
+
+
+def bucket_sizes(max_batch: int, num_graphs: int) -> List[int]:
+    """``unique(round(linspace(1, max_batch, max(2, num_graphs))))`` (generate.py:301-316)."""
+    n = max(2, num_graphs)
+    if max_batch <= 1:
+        return [1]
+    sizes = {int(round(1 + i * (max_batch - 1) / (n - 1))) for i in range(n)}
+    return sorted(sizes)
+
+
+class _Bucket:
+    def __init__(self, size: int, device) -> None:
+        self.size = size
+        # one packed buffer: tokens | pos | req | arange | ones
+        self.host = torch.empty(3 * size, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(5 * size, dtype=torch.int32, device=device)
+        self.dev[3 * size : 4 * size] = torch.arange(size, dtype=torch.int32, device=device)
+        self.dev[4 * size :] = 1
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.n_kernels = 0
+
+    def context(self, device) -> StepContext:
+        n = self.size
+        ctx = StepContext(device)
+        ctx.tokens, ctx.pos, ctx.req = self.dev[:n], self.dev[n : 2 * n], self.dev[2 * n : 3 * n]
+        ctx.want_rows = self.dev[3 * n : 4 * n]
+        ctx.seq_slot = ctx.req
+        ctx.n_tokens = ctx.n_seqs = ctx.n_want = n
+        tiles = AttentionTiles(ctx.req, self.dev[3 * n : 4 * n], self.dev[4 * n :], n)
+        ctx.attention_tiles = lambda n_heads, n_kv_heads: tiles  # one token per tile, whatever the grouping
+        ctx.decode_only = True
+        return ctx
+
+
+class DecodeGraphs:
+    def __init__(self, engine, max_batch: int, num_graphs: int) -> None:
+        self.engine = engine
+        self.sizes = bucket_sizes(max_batch, num_graphs)
+        self.buckets: Dict[int, _Bucket] = {}
+        self.pool = None
+        self.replays = 0
+
+    def run(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int]) -> torch.Tensor:
+        """Logits [len(tokens), vocab] of one decode step."""
+        n = len(tokens)
+        size = self.sizes[bisect.bisect_left(self.sizes, n)]
+        b = self.buckets.get(size)
+        if b is None:
+            b = self.buckets[size] = _Bucket(size, self.engine.device)
+        host = b.host.numpy()
+        host[:n] = tokens
+        host[n:size] = 0
+        host[size : size + n] = positions
+        host[size + n : 2 * size] = 0
+        host[2 * size : 2 * size + n] = slots
+        host[2 * size + n :] = -1
+        b.dev[: 3 * size].copy_(b.host, non_blocking=True)
+        model, memories = self.engine.model, self.engine.memories
+        if b.graph is None:
+            ctx = b.context(self.engine.device)
+            # once eagerly (libraries load, attributes get set), then capture
+            model.forward(ctx, memories)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = Ops.launches
+            with torch.cuda.graph(graph, pool=self.pool):
+                b.logits = model.forward(ctx, memories)
+            b.n_kernels = Ops.launches - before
+            if self.pool is None:
+                self.pool = graph.pool()
+            b.graph = graph
+        b.graph.replay()
+        Ops.launches += b.n_kernels
+        self.replays += 1
+        return b.logits[:n]

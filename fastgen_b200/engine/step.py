@@ -14,12 +14,20 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages, RequestCache
 from ..csrc.ops import attention_tiling
 from .model import Model
+
+
+def _decode_graphs():
+    from .decode_graph import DecodeGraphs
+
+    return DecodeGraphs
 
 
 @dataclass
@@ -95,6 +103,8 @@ class Engine:
         n_pages: int,
         max_requests: int,
         max_length: Optional[int] = None,
+        num_cuda_graphs: int = 16,
+        use_graphs: Optional[bool] = None,
     ) -> None:
         self.model = model
         self.ops = model.ops
@@ -116,6 +126,10 @@ class Engine:
             device=self.device,
         )
         self.memories = [self.cache.memory(e) for e in range(len(args.schedule))]
+        if use_graphs is None:
+            use_graphs = not bool(os.environ.get("FG_NO_CUDA_GRAPHS"))
+        # steps of single tokens replay a captured graph (as generate.py:296-347)
+        self.graphs = _decode_graphs()(self, max_requests, num_cuda_graphs) if use_graphs else None
 
     # -- requests --------------------------------------------------------------
     def admit(self, request_id) -> RequestCache:
@@ -229,5 +243,9 @@ class Engine:
 
     def _run(self, entries, reqs) -> Optional[torch.Tensor]:
         self.cache.flush_tables()
+        if self.graphs is not None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self.graphs.run(
+                [int(e.tokens[0]) for e in entries], [r.length for r in reqs], [r.slot for r in reqs]
+            )
         ctx = self.build_context(entries, reqs)
         return self.model.forward(ctx, self.memories)
