@@ -1,0 +1,301 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens/s and prefill tokens/s of a Llama-3.1-8B-shaped model.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step.  The default run has the layer sizes of Llama 3.1 8B
+with random weights, a batch of 8 and a context of 4,096 tokens: the timed
+steps end at position 4,096.  One JSON line is printed (see the keys below).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import queue
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA_8B = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=14336,
+    num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5,
+    vocab_size=128256, tie_word_embeddings=False, rope_theta=500000.0,
+    rope_scaling=dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192, rope_type="llama3"),
+    max_position_embeddings=131072,
+)
+PAGE = 64
+SEED = 4
+PREFILL_TOKENS = 2048
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        p = json.loads(path.read_text())
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.proc = None
+        self.lines = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=mx, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def model_flops(cfg: dict, n_layers: int, t: int, rows: int) -> float:
+    """FLOPs of a whole-prompt step of t tokens with logits at `rows` places."""
+    d, f, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    hq, hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    hd = d // hq
+    per_layer = 2 * t * d * (hq + 2 * hkv) * hd + 2 * t * hq * hd * d + 3 * 2 * t * d * f
+    attn = 4 * hd * hq * t * (t + 1) / 2
+    return n_layers * (per_layer + attn) + 2 * rows * d * v
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from fastgen_b200.config import model_args_from_config
+    from fastgen_b200.csrc.ops import Ops
+    from fastgen_b200.engine import Engine, Fastgen, GenArgs, Model, Packet, StepEntry
+    from fastgen_b200.sampling import Sampler
+
+    pk = peaks()
+    cfg = dict(LLAMA_8B)
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or full_layers
+    n_layers = cfg["num_hidden_layers"]
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    margs = model_args_from_config(cfg)
+    model = Model.random(margs, torch.bfloat16, dev, seed=SEED)
+    vocab = cfg["vocab_size"]
+    ctx_len = args.context
+    k, w = args.steps, args.warmup
+    prompt_len = max(1, ctx_len - k - w)
+    max_b = max(args.batch, 64 if not args.skip_points else args.batch, 1)
+    n_pages = max_b * (-(-(ctx_len + 1) // PAGE)) + PREFILL_TOKENS // PAGE + 1
+    engine = Engine(model, page_size=PAGE, n_pages=n_pages, max_requests=max_b,
+                    max_length=ctx_len + PAGE, num_cuda_graphs=max_b)
+    sampler = Sampler(model.ops, vocab, max_b, use_sampling=False)
+    gen = torch.Generator().manual_seed(SEED)
+
+    def prompt(n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+    def event_ms(fn, reps):
+        times = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        return times
+
+    # ---- prefill of 2,048 tokens (one whole prompt, logits at its last token) ----
+    toks = prompt(PREFILL_TOKENS)
+
+    def prefill_once():
+        engine.admit("p")
+        engine.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])])
+        engine.release("p")
+
+    for _ in range(3):
+        prefill_once()
+    pre_ms = min(event_ms(prefill_once, 5))
+    pre_flops = model_flops(cfg, n_layers, PREFILL_TOKENS, 1)
+    prefill = dict(value=round(PREFILL_TOKENS / pre_ms * 1e3, 1), tokens=PREFILL_TOKENS, ms=round(pre_ms, 3),
+                   frac=round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                   tflops=round(pre_flops / (pre_ms * 1e-3) / 1e12, 1), peak_tflops=pk["bf16_tflops"])
+
+    # ---- decode, device-timed: K graph replays + sampling, tokens stay on the device ----
+    weight_bytes = model.weight_bytes()  # every matrix once; the embedding table only if it is the output
+    kv_per_token = model.cache_bytes_per_token(2)
+
+    def decode_run(batch, steps, warm, clocks=None):
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            engine.admit(rid)
+        for rid in ids:  # fill the cache: the prompt in portions of 2,048
+            p = prompt(prompt_len)
+            for s in range(0, prompt_len, PREFILL_TOKENS):
+                engine.step([StepEntry(rid, p[s:s + PREFILL_TOKENS], [])])
+        reqs = [engine.cache.get(rid) for rid in ids]
+        slots = [r.slot for r in reqs]
+        tokens = torch.randint(0, vocab, (batch,), generator=gen).to(dev, torch.int32)
+        launches0 = None
+
+        def one_step():
+            nonlocal tokens
+            for r in reqs:
+                engine.cache.reserve(r, r.length + 1)
+            engine.cache.flush_tables()
+            logits = engine.graphs.run(tokens, [r.length for r in reqs], slots)
+            tokens, _ = sampler.sample(logits, [0.0] * batch, [0] * batch, [0] * batch)
+            for r in reqs:
+                engine.cache.advance(r, r.length + 1)
+
+        for _ in range(warm):
+            one_step()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.start()
+        launches0 = Ops.launches
+        first_len = reqs[0].length
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            one_step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        clk = clocks.stop() if clocks else None
+        launches = Ops.launches - launches0
+        last_len = reqs[0].length
+        engine.ops.check_status()
+        for rid in ids:
+            engine.release(rid)
+        avg_ctx = (first_len + last_len) / 2
+        step_bytes = weight_bytes + batch * avg_ctx * kv_per_token
+        return dict(ms_per_step=ms / steps, tok_s=batch * steps / ms * 1e3, launches=launches,
+                    gbs=step_bytes / (ms / steps * 1e-3) / 1e9, clocks=clk, first=first_len, last=last_len)
+
+    clocks = ClockSampler()
+    main = decode_run(args.batch, k, w, clocks)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = decode_run(b, min(k, 128), w)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / pk["hbm_gbs"], 4)
+    points[f"decode_b{args.batch}"] = round(main["tok_s"], 1)
+
+    # ---- the same through the Python entry point: host tokens in, host tokens out ----
+    del engine
+    torch.cuda.empty_cache()
+    fg = Fastgen(GenArgs(use_sampling=False, max_batch=args.batch, max_seq=args.batch * (ctx_len + PAGE),
+                         max_gen=k + w, cache_block=PAGE, max_prefill=PREFILL_TOKENS,
+                         num_cuda_graphs=args.batch), model, stop_tokens=[])
+    q = queue.Queue()
+    for i in range(args.batch):
+        q.put(Packet(thread_id=i, tokens=prompt(prompt_len)))
+    q.put(None)
+    n_out = sum(len(p.tokens) for p in fg.generate(q))
+    log = [s for s in fg.step_log if s["prompt_tokens"] == 0 and s["decode_tokens"] == args.batch]
+    tail = log[-k:] if len(log) > k else log[1:]
+    e2e_tokens = sum(s["decode_tokens"] for s in tail)
+    e2e_s = tail[-1]["t_end"] - tail[0]["t_start"]
+    e2e = dict(value=round(e2e_tokens / e2e_s, 1), unit="tokens/s",
+               h2d_bytes_per_step=int(sum(s["h2d_bytes"] for s in tail) / len(tail)),
+               d2h_bytes_per_step=int(sum(s["d2h_bytes"] for s in tail) / len(tail)),
+               steps=len(tail), generated=n_out)
+    fg.destroy()
+
+    return {
+        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (8B, bf16)",
+        "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": k, "warmup": w,
+        "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights seed 4, uniform random token ids)",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.1-8B shape", "global_batch": args.batch, "seq_len": ctx_len,
+            "parallelism": "single GPU", "layers": n_layers, "layers_full": full_layers,
+            "hidden": cfg["hidden_size"], "ffn": cfg["intermediate_size"], "q_heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": 128, "vocab": vocab, "page": PAGE,
+            "decode_from": main["first"], "decode_to": main["last"], "prefill_tokens": PREFILL_TOKENS,
+            "l2": "inputs larger than L2 (all weights are streamed every step)", "peaks": pk["source"],
+        },
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(main["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main["gbs"] / pk["hbm_gbs"], 4)},
+        "points": points,
+        "e2e": e2e,
+        "gpu_launches": main["launches"],
+        "clocks": main["clocks"],
+    }
+
+
+def run_reference(args) -> dict:
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        from reference_arm import run
+    except Exception as e:  # the arm's own module is missing or broken
+        return {"impl": "reference", "unavailable": f"reference arm not runnable: {e!r}"[:300]}
+    return run(args, LLAMA_8B)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -29,11 +29,18 @@ def bucket_sizes(max_batch: int, num_graphs: int) -> List[int]:
     return sorted(sizes)
 
 
+_RING = 8
+
+
 class _Bucket:
     def __init__(self, size: int, device) -> None:
         self.size = size
         # one packed buffer: tokens | pos | req | arange | ones
-        self.host = torch.empty(3 * size, dtype=torch.int32).pin_memory()
+        # a ring of pinned staging buffers: a buffer is rewritten only after the
+        # copy that last read it has run, so the host may run ahead of the device
+        self.ring = [torch.empty(3 * size, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.ring_events = [None] * _RING
+        self.ring_next = 0
         self.dev = torch.zeros(5 * size, dtype=torch.int32, device=device)
         self.dev[3 * size : 4 * size] = torch.arange(size, dtype=torch.int32, device=device)
         self.dev[4 * size :] = 1
@@ -61,22 +68,38 @@ class DecodeGraphs:
         self.buckets: Dict[int, _Bucket] = {}
         self.pool = None
         self.replays = 0
+        self.last_h2d_bytes = 0
 
-    def run(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int]) -> torch.Tensor:
-        """Logits [len(tokens), vocab] of one decode step."""
-        n = len(tokens)
+    def run(self, tokens, positions: Sequence[int], slots: Sequence[int]) -> torch.Tensor:
+        """Logits [n, vocab] of one decode step.  ``tokens`` is a list of ids, or
+        a device int32 tensor (the previous step's samples, which then never
+        visit the host)."""
+        n = len(positions)
         size = self.sizes[bisect.bisect_left(self.sizes, n)]
         b = self.buckets.get(size)
         if b is None:
             b = self.buckets[size] = _Bucket(size, self.engine.device)
-        host = b.host.numpy()
-        host[:n] = tokens
-        host[n:size] = 0
+        slot = b.ring_next
+        b.ring_next = (slot + 1) % _RING
+        if b.ring_events[slot] is not None:
+            b.ring_events[slot].synchronize()
+        staging = b.ring[slot]
+        host = staging.numpy()
         host[size : size + n] = positions
         host[size + n : 2 * size] = 0
         host[2 * size : 2 * size + n] = slots
         host[2 * size + n :] = -1
-        b.dev[: 3 * size].copy_(b.host, non_blocking=True)
+        if isinstance(tokens, torch.Tensor):
+            b.dev[size : 3 * size].copy_(staging[size:], non_blocking=True)
+            b.dev[:n].copy_(tokens[:n])
+        else:
+            host[:n] = tokens
+            host[n:size] = 0
+            b.dev[: 3 * size].copy_(staging, non_blocking=True)
+        self.last_h2d_bytes = 4 * (2 * size if isinstance(tokens, torch.Tensor) else 3 * size)
+        ev = torch.cuda.Event()
+        ev.record()
+        b.ring_events[slot] = ev
         model, memories = self.engine.model, self.engine.memories
         if b.graph is None:
             ctx = b.context(self.engine.device)

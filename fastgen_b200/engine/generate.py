@@ -151,6 +151,7 @@ class Fastgen:
             self.engine.cache, self.max_batch, self.max_prefill, self.stop_tokens, args.max_gen
         )
         self.steps = 0
+        self.step_log: List[dict] = []  # per step: times, token counts, bytes copied
 
     def destroy(self) -> None:
         """Free what the generator holds on the device."""
@@ -215,6 +216,7 @@ class Fastgen:
                 StepEntry(id(e.request), e.tokens, [len(e.tokens) - 1] if e.samples else [])
                 for e in plan
             ]
+            t_start = time.perf_counter()
             logits = self.engine.step_reserved(entries)
             self.steps += 1
             sampling = [e for e in plan if e.samples]
@@ -229,5 +231,13 @@ class Fastgen:
                 )
                 tokens = out.tolist()  # the step's one device-to-host read
                 logprobs = lp.tolist() if lp is not None else None
+            n_decode = sum(1 for e in plan if len(e.tokens) == 1 and e.samples and e.request.generated)
+            self.step_log.append(dict(
+                t_start=t_start, t_end=time.perf_counter(), decode_tokens=n_decode,
+                prompt_tokens=sum(len(e.tokens) for e in plan) - n_decode,
+                h2d_bytes=self.engine.last_h2d_bytes, d2h_bytes=4 * len(tokens),
+            ))
+            if len(self.step_log) > 100_000:
+                del self.step_log[:50_000]
             for req in sched.commit(plan, tokens, logprobs):
                 yield self._packet(req)

@@ -148,6 +148,27 @@ class Model:
         del tensors
         return model
 
+    @staticmethod
+    def random(args: ModelArgs, dtype: torch.dtype, device, seed: int = 0) -> "Model":
+        """A model with seeded random weights drawn on the device (no files):
+        matrices N(0, 0.02), norm weights 1, as the random-weights writer does."""
+        from ..csrc.ops import Ops
+
+        model = Model(args, Ops(dtype, device))
+        gen = torch.Generator(device=device).manual_seed(int(seed))
+        tensors = {}
+        for spec in model.weight_specs():
+            if spec.init[0] == "normal":
+                t = torch.empty(spec.shape, dtype=torch.bfloat16, device=device)
+                t.normal_(0.0, spec.init[1], generator=gen)
+            elif spec.init[0] == "ones":
+                t = torch.ones(spec.shape, dtype=torch.bfloat16, device=device)
+            else:
+                t = torch.randint(0, spec.init[1], spec.shape, generator=gen, device=device, dtype=torch.int32)
+            tensors[spec.name] = t
+        model.bind(tensors)
+        return model
+
     # -- forward -----------------------------------------------------------------
     def forward(self, ctx, memories) -> Optional[torch.Tensor]:
         """Run the step's tokens through the schedule.  Returns float32 logits

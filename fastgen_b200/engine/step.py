@@ -126,6 +126,7 @@ class Engine:
             device=self.device,
         )
         self.memories = [self.cache.memory(e) for e in range(len(args.schedule))]
+        self.last_h2d_bytes = 0
         if use_graphs is None:
             use_graphs = not bool(os.environ.get("FG_NO_CUDA_GRAPHS"))
         # steps of single tokens replay a captured graph (as generate.py:296-347)
@@ -198,6 +199,7 @@ class Engine:
             ]
         )
         dev = torch.from_numpy(packed).to(self.device)
+        self.last_h2d_bytes = packed.nbytes
         o = 0
         ctx.tokens, o = dev[o : o + t], o + t
         ctx.pos, o = dev[o : o + t], o + t
@@ -244,8 +246,10 @@ class Engine:
     def _run(self, entries, reqs) -> Optional[torch.Tensor]:
         self.cache.flush_tables()
         if self.graphs is not None and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self.graphs.run(
+            logits = self.graphs.run(
                 [int(e.tokens[0]) for e in entries], [r.length for r in reqs], [r.slot for r in reqs]
             )
+            self.last_h2d_bytes = self.graphs.last_h2d_bytes
+            return logits
         ctx = self.build_context(entries, reqs)
         return self.model.forward(ctx, self.memories)
