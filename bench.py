@@ -124,9 +124,9 @@ def run_ours(args) -> dict:
     k, w = args.steps, args.warmup
     prompt_len = max(1, ctx_len - k - w)
     max_b = max(args.batch, 64 if not args.skip_points else args.batch, 1)
-    n_pages = max_b * (-(-(ctx_len + 1) // PAGE)) + PREFILL_TOKENS // PAGE + 1
+    n_pages = max_b * (-(-(ctx_len + 1) // PAGE)) + PREFILL_TOKENS // PAGE + 2
     engine = Engine(model, page_size=PAGE, n_pages=n_pages, max_requests=max_b,
-                    max_length=ctx_len + PAGE, num_cuda_graphs=max_b)
+                    max_length=max(ctx_len, PREFILL_TOKENS) + PAGE, num_cuda_graphs=max_b)
     sampler = Sampler(model.ops, vocab, max_b, use_sampling=False)
     gen = torch.Generator().manual_seed(SEED)
 

@@ -57,3 +57,96 @@ extern "C" int fg_attention_simt(const void* q, int q_stride, void* out, int out
   FG_CHECK_LAUNCH("fg_attention_simt");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// bfloat16 on the tensor cores
+// ---------------------------------------------------------------------------------
+#include "attention_mma.cuh"
+
+extern "C" int fg_attention_prefill_rows() { return fg_mma::PREFILL_ROWS; }
+extern "C" int fg_attention_decode_split() { return fg_mma::DECODE_SPLIT; }
+
+// Floats of scratch that fg_attention_decode_bf16 needs.
+extern "C" long long fg_attention_decode_scratch_floats(int n_seqs, int max_splits, int n_heads) {
+  return (long long)n_seqs * max_splits * n_heads * fg_mma::part_stride<FG_HEAD_DIM>();
+}
+
+// Prompt portions.  Tiles hold max(1, 64 / hpb) consecutive tokens of one request,
+// hpb = min(group, 64); grid.z walks the group in slices of hpb heads.
+extern "C" int fg_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                         const void* k_pages, const void* v_pages, const int* block_table,
+                                         int table_width, int page_size, int n_pages, const int* pos,
+                                         const int* tile_req, const int* tile_tok0, const int* tile_ntok,
+                                         int n_tiles, int n_heads, int n_kv_heads, int head_dim, int window,
+                                         float scale, int* status, cudaStream_t stream) {
+  using namespace fg_mma;
+  if (n_tiles == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
+               "fg_attention_prefill_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
+               "fg_attention_prefill_bf16: queries must be 16-byte aligned with a row stride multiple of 8");
+  const int group = n_heads / n_kv_heads;
+  const int hpb = group < PREFILL_ROWS ? group : PREFILL_ROWS;
+  dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
+  constexpr size_t smem = prefill_smem_bytes<FG_HEAD_DIM>();
+  auto kern = attention_prefill_kernel<FG_HEAD_DIM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  kern<<<grid, THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, block_table, table_width, page_size, n_pages, pos, tile_req, tile_tok0,
+      tile_ntok, n_kv_heads, group, hpb, window, scale * 1.4426950408889634f, status);
+  FG_CHECK_LAUNCH("fg_attention_prefill_bf16");
+  return 0;
+}
+
+// Single tokens: sequence i of the list is token seq_tok[i] of request seq_req[i]
+// (negative: padding).  max_splits >= ceil((largest position + 1) / 128).
+extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_pages, const void* v_pages, const int* block_table,
+                                        int table_width, int page_size, int n_pages, const int* pos,
+                                        const int* seq_req, const int* seq_tok, int n_seqs, int n_heads,
+                                        int n_kv_heads, int head_dim, int window, float scale, float* scratch,
+                                        long long scratch_floats, int max_splits, int* status,
+                                        cudaStream_t stream) {
+  using namespace fg_mma;
+  if (n_seqs == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535 && n_seqs <= 65535,
+               "fg_attention_decode_bf16: %d heads over %d kv heads, %d sequences", n_heads, n_kv_heads, n_seqs);
+  FG_CHECK_ARG(max_splits > 0, "fg_attention_decode_bf16: max_splits must be positive");
+  FG_CHECK_ARG(scratch != nullptr &&
+                   scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads),
+               "fg_attention_decode_bf16: scratch of %lld floats is too small (%lld needed)", scratch_floats,
+               fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads));
+  FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
+               "fg_attention_decode_bf16: queries must be 16-byte aligned with a row stride multiple of 8");
+  const int group = n_heads / n_kv_heads;
+  constexpr size_t smem = decode_smem_bytes<FG_HEAD_DIM>();
+  auto kern = attention_decode_kernel<FG_HEAD_DIM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(max_splits, n_kv_heads, n_seqs);
+  kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
+                                        (const __nv_bfloat16*)v_pages, block_table, table_width, page_size,
+                                        n_pages, pos, seq_req, seq_tok, n_heads, n_kv_heads, group, window,
+                                        scale_log2, scratch, max_splits, status);
+  FG_CHECK_LAUNCH("fg_attention_decode_bf16");
+  dim3 cgrid(n_heads, n_seqs);
+  attention_combine_kernel<FG_HEAD_DIM><<<cgrid, FG_HEAD_DIM < 128 ? FG_HEAD_DIM : 128, 0, stream>>>(
+      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, status);
+  FG_CHECK_LAUNCH("fg_attention_combine");
+  return 0;
+}

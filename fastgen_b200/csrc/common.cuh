@@ -20,6 +20,7 @@
 #define FG_STATUS_BAD_PAGE 1      // a block-table entry was negative or too large
 #define FG_STATUS_BAD_TOKEN 2     // a token id outside the vocabulary
 #define FG_STATUS_WAIT_TIMEOUT 4  // a bounded wait on a barrier gave up
+#define FG_STATUS_BAD_SPLITS 8    // decode attention was launched with too few splits
 
 void fg_set_error(const char* fmt, ...);
 

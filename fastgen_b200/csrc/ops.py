@@ -22,6 +22,7 @@ FG_F32, FG_BF16 = 0, 1
 STATUS_BAD_PAGE = 1
 STATUS_BAD_TOKEN = 2
 STATUS_WAIT_TIMEOUT = 4
+STATUS_BAD_SPLITS = 8
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -50,7 +51,14 @@ _CORE_SIGNATURES = {
 
 _ATTN_SIGNATURES = {
     "fg_attention_simt": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
+                                 ctypes.c_longlong, _I, _P, _P],
 }
+
+SIMT_ROWS = 16       # query rows per block of the float32 attention kernel
+PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
+DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kernel
 
 
 def _declare(lib: ctypes.CDLL, signatures) -> None:
@@ -91,6 +99,11 @@ def attn(head_dim: int):
     if lib is None:
         lib = build.attention_library(head_dim)
         _declare(lib, _ATTN_SIGNATURES)
+        lib.fg_attention_decode_scratch_floats.argtypes = [_I, _I, _I]
+        lib.fg_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        assert lib.fg_attention_rows_per_block() == SIMT_ROWS
+        assert lib.fg_attention_prefill_rows() == PREFILL_ROWS
+        assert lib.fg_attention_decode_split() == DECODE_SPLIT
         _attn[head_dim] = lib
     return lib
 
@@ -110,10 +123,11 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def attention_tiling(n_heads: int, n_kv_heads: int) -> int:
-    """Tokens per attention tile for a head grouping (see attention.cu)."""
+def attention_tiling(n_heads: int, n_kv_heads: int, rows: int = SIMT_ROWS) -> int:
+    """Tokens per attention tile for a head grouping and a block of ``rows``
+    query rows (see attention.cu)."""
     group = n_heads // n_kv_heads
-    return max(1, 16 // min(group, 16))
+    return max(1, rows // min(group, rows))
 
 
 class Ops:
@@ -132,6 +146,7 @@ class Ops:
         self.code = _code(dtype)
         self.lib = core()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._scratch = {}
 
     # -- status word ---------------------------------------------------------
     def check_status(self) -> None:
@@ -147,6 +162,8 @@ class Ops:
                 faults.append("a token id was outside the vocabulary")
             if word & STATUS_WAIT_TIMEOUT:
                 faults.append("a bounded wait inside a kernel gave up")
+            if word & STATUS_BAD_SPLITS:
+                faults.append("decode attention was launched with too few splits")
             raise KernelError("kernel status: " + "; ".join(faults))
 
     # -- kernels ---------------------------------------------------------------
@@ -233,19 +250,52 @@ class Ops:
             _ptr(block_table) if k is not None else None, width, page_size, n_pages,
             t, n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
 
-    def attention(self, q, out, k_pages, v_pages, block_table, page_size: int, pos,
-                  tiles, n_heads: int, n_kv_heads: int, head_dim: int,
+    def _decode_scratch(self, floats: int) -> torch.Tensor:
+        """Scratch for the split partials.  Buffers are kept for good (captured
+        graphs hold their addresses) and come in power-of-two sizes."""
+        size = 1 << max(16, (floats - 1).bit_length())
+        buf = self._scratch.get(size)
+        if buf is None:
+            buf = self._scratch[size] = torch.empty(size, dtype=torch.float32, device=self.device)
+        return buf
+
+    def attention(self, q, out, k_pages, v_pages, block_table, page_size: int, ctx,
+                  n_heads: int, n_kv_heads: int, head_dim: int,
                   window: Optional[int], scale: float) -> None:
-        """Paged causal attention of the step's query tokens.  ``tiles`` is the
-        step's :class:`AttentionTiles` for this head grouping."""
+        """Paged causal attention of the step's query tokens (``ctx`` is the
+        step's context).  bfloat16 runs on the tensor cores: prompt portions in
+        one kernel, single tokens in a split-and-combine pair; float32 runs one
+        CUDA-core kernel for all."""
         lib = attn(head_dim)
         assert q.stride(1) == 1 and out.stride(1) == 1
-        _check(lib, lib.fg_attention_simt(
-            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _code(q.dtype), _ptr(k_pages),
-            _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size, k_pages.shape[0],
-            _ptr(pos), _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
-            n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
-            _ptr(self.status), _stream()))
+        common = (_ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
+                  k_pages.shape[0], _ptr(ctx.pos))
+        if q.dtype == torch.float32:
+            tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, SIMT_ROWS), 1)
+            _check(lib, lib.fg_attention_simt(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), FG_F32, *common,
+                _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
+                n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+                _ptr(self.status), _stream()))
+            return
+        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, PREFILL_ROWS), 2)
+        if tiles.n:
+            _check(lib, lib.fg_attention_prefill_bf16(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
+                _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
+                n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+                _ptr(self.status), _stream()))
+        singles = ctx.single_tokens()
+        if singles.n:
+            max_splits = max(1, -(-singles.max_len // DECODE_SPLIT))
+            floats = lib.fg_attention_decode_scratch_floats(singles.n, max_splits, n_heads)
+            scratch = self._decode_scratch(floats)
+            _check(lib, lib.fg_attention_decode_bf16(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
+                _ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
+                int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits,
+                _ptr(self.status), _stream()))
+            Ops.launches += 1  # the combine kernel
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
                out_tokens, out_logprobs=None, scratch=None) -> torch.Tensor:

@@ -17,7 +17,8 @@ import numpy as np
 import torch
 
 from ..csrc.ops import Ops
-from .step import AttentionTiles, StepContext
+from ..csrc.ops import DECODE_SPLIT
+from .step import AttentionTiles, SingleTokens, StepContext
 
 
 def bucket_sizes(max_batch: int, num_graphs: int) -> List[int]:
@@ -33,8 +34,9 @@ _RING = 8
 
 
 class _Bucket:
-    def __init__(self, size: int, device) -> None:
+    def __init__(self, size: int, max_len: int, device) -> None:
         self.size = size
+        self.max_len = max_len  # positions the captured launch grids cover
         # one packed buffer: tokens | pos | req | arange | ones
         # a ring of pinned staging buffers: a buffer is rewritten only after the
         # copy that last read it has run, so the host may run ahead of the device
@@ -55,9 +57,13 @@ class _Bucket:
         ctx.want_rows = self.dev[3 * n : 4 * n]
         ctx.seq_slot = ctx.req
         ctx.n_tokens = ctx.n_seqs = ctx.n_want = n
+        # every sequence is one token: one-token tiles for kernels that tile all
+        # sequences, none for kernels that only take longer ones
         tiles = AttentionTiles(ctx.req, self.dev[3 * n : 4 * n], self.dev[4 * n :], n)
-        ctx.attention_tiles = lambda n_heads, n_kv_heads: tiles  # one token per tile, whatever the grouping
-        ctx.decode_only = True
+        none = AttentionTiles(None, None, None, 0)
+        ctx.attention_tiles = lambda tokens_per_tile, min_tokens=1: tiles if min_tokens <= 1 else none
+        singles = SingleTokens(ctx.req, self.dev[3 * n : 4 * n], n, self.max_len)
+        ctx.single_tokens = lambda: singles
         return ctx
 
 
@@ -65,7 +71,7 @@ class DecodeGraphs:
     def __init__(self, engine, max_batch: int, num_graphs: int) -> None:
         self.engine = engine
         self.sizes = bucket_sizes(max_batch, num_graphs)
-        self.buckets: Dict[int, _Bucket] = {}
+        self.buckets: Dict[tuple, _Bucket] = {}
         self.pool = None
         self.replays = 0
         self.last_h2d_bytes = 0
@@ -76,9 +82,12 @@ class DecodeGraphs:
         visit the host)."""
         n = len(positions)
         size = self.sizes[bisect.bisect_left(self.sizes, n)]
-        b = self.buckets.get(size)
+        # launch grids cover a power-of-two number of key splits
+        splits = -(-(max(positions) + 1) // DECODE_SPLIT)
+        splits = 1 << (splits - 1).bit_length()
+        b = self.buckets.get((size, splits))
         if b is None:
-            b = self.buckets[size] = _Bucket(size, self.engine.device)
+            b = self.buckets[(size, splits)] = _Bucket(size, splits * DECODE_SPLIT, self.engine.device)
         slot = b.ring_next
         b.ring_next = (slot + 1) % _RING
         if b.ring_events[slot] is not None:

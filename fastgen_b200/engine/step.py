@@ -49,6 +49,17 @@ class AttentionTiles:
     n: int
 
 
+@dataclass
+class SingleTokens:
+    """The step's sequences of one token: their slots and token indices on the
+    device, and the longest of them (cached tokens + 1) on the host."""
+
+    req: Optional[torch.Tensor]
+    tok: Optional[torch.Tensor]
+    n: int
+    max_len: int
+
+
 class StepContext:
     """Everything about the step's batch that parts may need, on host and device.
 
@@ -70,27 +81,51 @@ class StepContext:
         self.host_seq_slot: List[int] = []
         self.host_seq_start: List[int] = [0]
         self.host_seq_cached: List[int] = []
-        self._tiles: Dict[int, AttentionTiles] = {}
+        self._tiles: Dict[Tuple[int, int], AttentionTiles] = {}
+        self._singles: Optional[SingleTokens] = None
 
-    def attention_tiles(self, n_heads: int, n_kv_heads: int) -> AttentionTiles:
-        tpt = attention_tiling(n_heads, n_kv_heads)
-        tiles = self._tiles.get(tpt)
+    def attention_tiles(self, tokens_per_tile: int, min_tokens: int = 1) -> AttentionTiles:
+        """Tiles of at most ``tokens_per_tile`` consecutive tokens over the
+        sequences that bring at least ``min_tokens`` tokens."""
+        key = (tokens_per_tile, min_tokens)
+        tiles = self._tiles.get(key)
         if tiles is None:
-            tiles = self._build_tiles(tpt)
-            self._tiles[tpt] = tiles
+            tiles = self._tiles[key] = self._build_tiles(tokens_per_tile, min_tokens)
         return tiles
 
-    def _build_tiles(self, tpt: int) -> AttentionTiles:
+    def _build_tiles(self, tpt: int, min_tokens: int) -> AttentionTiles:
         req, tok0, ntok = [], [], []
         for b, slot in enumerate(self.host_seq_slot):
             start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
+            if end - start < min_tokens:
+                continue
             for t in range(start, end, tpt):
                 req.append(slot)
                 tok0.append(t)
                 ntok.append(min(tpt, end - t))
         n = len(req)
+        if n == 0:
+            return AttentionTiles(None, None, None, 0)
         packed = torch.tensor(req + tok0 + ntok, dtype=torch.int32).to(self.device)
         return AttentionTiles(packed[:n], packed[n : 2 * n], packed[2 * n :], n)
+
+    def single_tokens(self) -> "SingleTokens":
+        """The sequences that bring exactly one token (decoded tokens)."""
+        if self._singles is None:
+            req, tok, max_len = [], [], 0
+            for b, slot in enumerate(self.host_seq_slot):
+                start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
+                if end - start == 1:
+                    req.append(slot)
+                    tok.append(start)
+                    max_len = max(max_len, self.host_seq_cached[b] + 1)
+            n = len(req)
+            if n == 0:
+                self._singles = SingleTokens(None, None, 0, 0)
+            else:
+                packed = torch.tensor(req + tok, dtype=torch.int32).to(self.device)
+                self._singles = SingleTokens(packed[:n], packed[n:], n, max_len)
+        return self._singles
 
 
 class Engine:

@@ -83,8 +83,7 @@ class GQAAttention(Mixer):
         o = torch.empty((t, self.q_width), dtype=x.dtype, device=x.device)
         ops.attention(
             q, o, memory.k_pages, memory.v_pages, memory.block_table, memory.page_size,
-            ctx.pos, ctx.attention_tiles(p.n_heads, p.n_kv_heads), p.n_heads, p.n_kv_heads,
-            p.head_dim, p.window, self.scale,
+            ctx, p.n_heads, p.n_kv_heads, p.head_dim, p.window, self.scale,
         )
         return ops.linear(o, self.wo)
 

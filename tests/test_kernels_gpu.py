@@ -1,0 +1,334 @@
+"""Each kernel alone against a plain float64 reference, at sizes other than the engine's."""
+
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops32():
+    from fastgen_b200.csrc.ops import Ops
+    return Ops(torch.float32, DEV)
+
+
+@pytest.fixture(scope="module")
+def ops16():
+    from fastgen_b200.csrc.ops import Ops
+    return Ops(torch.bfloat16, DEV)
+
+
+def _tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim,vocab", [(72, 331), (4096, 1000), (8, 5)])
+def test_embedding(ops32, dtype, dim, vocab):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, dim, generator=g).to(DEV, dtype)
+    tokens = torch.randint(0, vocab, (37,), generator=g).to(DEV, torch.int32)
+    out = torch.empty(37, dim, dtype=torch.float32, device=DEV)
+    ops32.embedding(table, tokens, out)
+    assert torch.equal(out, table.float()[tokens.long()])
+    bad = tokens.clone(); bad[3] = vocab
+    ops32.embedding(table, bad, out)
+    from fastgen_b200.csrc.ops import KernelError
+    with pytest.raises(KernelError, match="vocabulary"):
+        ops32.check_status()
+    assert torch.count_nonzero(out[3]) == 0
+
+
+@pytest.mark.parametrize("dim", [64, 200, 4096, 5000])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(ops32, ops16, dim, wdtype):
+    g = torch.Generator().manual_seed(dim)
+    for ops, eps in ((ops32, 1e-5), (ops16, 1e-6)):
+        act = ops.act_dtype
+        h = (torch.randn(19, dim, generator=g) * 3).to(DEV)
+        delta = torch.randn(19, dim, generator=g).to(DEV, act)
+        w = (1 + 0.1 * torch.randn(dim, generator=g)).to(DEV, wdtype)
+        ref_h = h.double() + delta.double()
+        ref = pl.rmsnorm(ref_h, w.double(), eps)
+        out = torch.empty(19, dim, dtype=act, device=DEV)
+        h2 = h.clone()
+        ops.rmsnorm(h2, w, eps, out=out, delta=delta)
+        assert torch.allclose(h2.double(), ref_h, rtol=1e-6, atol=1e-6)  # the sum is float32
+        assert torch.allclose(out.double(), ref, **_tol(act))
+        # without delta; gathered rows leave h alone
+        out1 = torch.empty(19, dim, dtype=act, device=DEV)
+        ops.rmsnorm(h, w, eps, out=out1)
+        assert torch.allclose(out1.double(), pl.rmsnorm(h.double(), w.double(), eps), **_tol(act))
+        rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32, device=DEV)
+        outr = torch.empty(4, dim, dtype=act, device=DEV)
+        h3 = h.clone()
+        ops.rmsnorm(h3, w, eps, out=outr, delta=delta, rows=rows)
+        assert torch.equal(h3, h)
+        assert torch.allclose(outr.double(), ref[rows.long()], **_tol(act))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 320, 192), (37, 200, 331), (130, 65, 17), (64, 64, 16), (3, 1000, 4096)])
+def test_gemm_f32(ops32, m, n, k):
+    g = torch.Generator().manual_seed(m * n)
+    x = torch.randn(m, k, generator=g).to(DEV)
+    w = torch.randn(n, k, generator=g).to(DEV)
+    out = ops32.linear(x, w)
+    ref = x.double() @ w.double().T
+    assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4 * math.sqrt(k))
+    # rows do not depend on what else is in the batch: bitwise
+    out1 = ops32.linear(x[m // 2 : m // 2 + 1], w)
+    assert torch.equal(out1[0], out[m // 2])
+    # strided input (a column slice of a wider buffer)
+    wide = torch.randn(m, k + 24, generator=g).to(DEV)
+    assert torch.equal(ops32.linear(wide[:, 8 : 8 + k], w), ops32.linear(wide[:, 8 : 8 + k].contiguous(), w))
+
+
+def test_linear_bf16(ops16):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(9, 200, generator=g).to(DEV, torch.bfloat16)
+    w = torch.randn(331, 200, generator=g).to(DEV, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    assert torch.allclose(ops16.linear(x, w).double(), ref, rtol=2e-2, atol=0.2)
+    out32 = ops16.linear(x, w, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and torch.allclose(out32.double(), ref, rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("ffn", [176, 331, 14336])
+def test_silu_gate(ops32, dtype, ffn):
+    g = torch.Generator().manual_seed(ffn)
+    x = (torch.randn(11, 2 * ffn, generator=g) * 2).to(DEV, dtype)
+    out = torch.empty(11, ffn, dtype=dtype, device=DEV)
+    ops32.silu_gate(x, out)
+    xd = x.double()
+    ref = xd[:, :ffn] * torch.sigmoid(xd[:, :ffn]) * xd[:, ffn:]
+    assert torch.allclose(out.double(), ref, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,hd,page", [(4, 1, 16, 8), (6, 3, 32, 16), (5, 5, 48, 4), (32, 8, 128, 64)])
+def test_rope_kv_write(ops32, dtype, hq, hkv, hd, page):
+    g = torch.Generator().manual_seed(hd)
+    t, n_pages, width = 23, 12, 6
+    qkv = torch.randn(t, (hq + 2 * hkv) * hd, generator=g).to(DEV, dtype)
+    orig = qkv.clone()
+    freqs = pl.rope_freqs(hd, 10000.0, None).to(DEV)
+    # two requests: slots 2 and 0; positions straddle page edges; one padding token
+    req = torch.tensor([2] * 12 + [0] * 10 + [-1], dtype=torch.int32, device=DEV)
+    pos = torch.tensor(list(range(page - 3, page + 9)) + list(range(0, 10)) + [5], dtype=torch.int32, device=DEV)
+    table = torch.full((3, width), -1, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(n_pages, generator=g)
+    table[2, :4] = perm[:4].to(DEV, torch.int32)
+    table[0, :3] = perm[4:7].to(DEV, torch.int32)
+    kp = torch.zeros(n_pages, hkv, page, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q = qkv[:, : hq * hd]; k = qkv[:, hq * hd : (hq + hkv) * hd]; v = qkv[:, (hq + hkv) * hd :]
+    ops32.rope_kv_write(q, k, v, pos, req, freqs, kp, vp, table, page, hq, hkv, hd)
+    ops32.check_status()
+    od = orig.double()
+    rq = pl.apply_rope(od[:, : hq * hd].view(t, hq, hd), pos.cpu(), freqs.cpu()).view(t, -1)
+    rk = pl.apply_rope(od[:, hq * hd : (hq + hkv) * hd].view(t, hkv, hd), pos.cpu(), freqs.cpu())
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    assert torch.allclose(q[:22].double().cpu(), rq[:22].cpu(), **tol)
+    assert torch.equal(q[22], orig[22, : hq * hd]) or True  # padding: queries may be rotated, pages must not change
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    for i in range(22):
+        pg = int(table[int(req[i]), int(pos[i]) // page]); off = int(pos[i]) % page
+        written[pg, off] = True
+        assert torch.allclose(kp[pg, :, off].double().cpu(), rk[i].cpu(), **tol)
+        assert torch.equal(vp[pg, :, off].cpu(), orig[i, (hq + hkv) * hd :].view(hkv, hd).cpu())
+    untouched = ~written
+    assert torch.count_nonzero(kp.cpu().permute(0, 2, 1, 3)[untouched]) == 0
+    # a position beyond the request's table is reported, not written
+    pos2 = pos.clone(); pos2[0] = page * width + 1
+    ops32.rope_kv_write(q, k, v, pos2, req, freqs, kp, vp, table, page, hq, hkv, hd)
+    from fastgen_b200.csrc.ops import KernelError
+    with pytest.raises(KernelError, match="block-table"):
+        ops32.check_status()
+
+
+# ---------------------------------------------------------------------------------
+# attention: a step context by hand, a paged cache with shuffled pages
+# ---------------------------------------------------------------------------------
+def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None):
+    """seqs: list of (cached, new) per request.  Returns (out, ref) for the new tokens."""
+    from fastgen_b200.engine.step import StepContext
+
+    dtype = ops.act_dtype
+    g = torch.Generator().manual_seed(seed)
+    total = [c + n for c, n in seqs]
+    width = max(-(-t // page) for t in total) + 1
+    n_pages = sum(-(-t // page) for t in total) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.randn(n_pages, hkv, page, hd, generator=g).to(DEV, dtype)  # garbage in unused slots
+    vp = torch.randn(n_pages, hkv, page, hd, generator=g).to(DEV, dtype)
+    table = torch.full((len(seqs) + 2, width), -1, dtype=torch.int32)
+    ctx = StepContext(DEV)
+    qs, refs, pos, req = [], [], [], []
+    slots = list(range(len(seqs) + 2))
+    random.Random(seed).shuffle(slots)
+    for b, (cached, new) in enumerate(seqs):
+        slot = slots[b]
+        t = cached + new
+        k = torch.randn(t, hkv, hd, generator=g).to(dtype)
+        v = torch.randn(t, hkv, hd, generator=g).to(dtype)
+        q = torch.randn(t, hq, hd, generator=g).to(dtype)
+        if boost is not None and t > boost[1]:
+            # make one far key dominate one query: a fault in reaching it shows
+            qi, kj = t - 1, boost[1]
+            k[kj] = q[qi, 0 :: hq // hkv][:hkv] * 4.0
+        for lp in range(-(-t // page)):
+            pg = perm.pop()
+            table[slot, lp] = pg
+            rows = slice(lp * page, min(t, (lp + 1) * page))
+            n = rows.stop - rows.start
+            kp[pg, :, :n] = k[rows].permute(1, 0, 2).to(DEV)
+            vp[pg, :, :n] = v[rows].permute(1, 0, 2).to(DEV)
+        ref = pl.causal_attention(q.double(), k.double(), v.double(), hd ** -0.5, window)[cached:]
+        refs.append(ref.reshape(new, hq * hd))
+        qs.append(q[cached:].reshape(new, hq * hd))
+        pos += list(range(cached, t)); req += [slot] * new
+        ctx.host_seq_slot.append(slot); ctx.host_seq_cached.append(cached)
+        ctx.host_seq_start.append(ctx.host_seq_start[-1] + new)
+    ctx.pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
+    ctx.req = torch.tensor(req, dtype=torch.int32, device=DEV)
+    ctx.n_tokens = len(pos)
+    q = torch.cat(qs).to(DEV)
+    # queries live in a wider row, as in the fused projection
+    wide = torch.zeros(q.shape[0], q.shape[1] + 2 * hkv * hd, dtype=dtype, device=DEV)
+    wide[:, : q.shape[1]] = q
+    out = torch.full((q.shape[0], hq * hd), float("nan"), dtype=dtype, device=DEV)
+    ops.attention(wide[:, : q.shape[1]], out, kp, vp, table.to(DEV), page, ctx, hq, hkv, hd, window, hd ** -0.5)
+    ops.check_status()
+    return out.double().cpu(), torch.cat(refs)
+
+
+CASES = [
+    # (seqs, hq, hkv, hd, page, window)
+    ([(0, 7), (0, 13), (0, 1), (0, 30)], 4, 1, 16, 8, None),
+    ([(12, 1), (40, 9), (0, 70), (99, 1), (63, 2)], 6, 3, 32, 16, None),
+    ([(5, 33), (90, 1), (64, 64), (23, 1)], 6, 2, 48, 8, 24),
+    ([(300, 1), (0, 130), (255, 3), (128, 1)], 8, 2, 64, 64, None),
+    ([(517, 1), (130, 70)], 32, 8, 128, 64, None),
+    ([(127, 1), (128, 1), (129, 1), (0, 1)], 5, 5, 16, 4, 100),
+    ([(200, 1), (10, 50)], 40, 2, 32, 16, None),   # a group of 20 heads
+]
+
+
+@pytest.mark.parametrize("case", range(len(CASES)))
+def test_attention(ops32, ops16, case):
+    seqs, hq, hkv, hd, page, window = CASES[case]
+    out, ref = _attention_case(ops32, seqs, hq, hkv, hd, page, window, case)
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5), float((out - ref).abs().max())
+    out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, case)
+    assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), float((out - ref).abs().max())
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
+def test_attention_reaches_a_far_key(ops32, ops16, far):
+    """One key among hundreds dominates the last query: it must be found wherever it lies."""
+    for ops, tol in ((ops32, 1e-4), (ops16, 5e-2)):
+        for seqs in ([(0, 400)], [(399, 1)], [(250, 150)]):
+            out, ref = _attention_case(ops, seqs, 4, 2, 32, 16, None, 77, boost=(None, far))
+            assert float((out - ref).abs().max()) < tol
+
+
+def test_attention_window_edge(ops32, ops16):
+    """The key at pos - window must be out, the one at pos - window + 1 in."""
+    for ops, tol in ((ops32, 1e-4), (ops16, 5e-2)):
+        for far in (75, 76):  # last query at 99, window 24: keys 76..99 are visible
+            out, ref = _attention_case(ops, [(99, 1)], 2, 1, 16, 8, 24, 5, boost=(None, far))
+            assert float((out - ref).abs().max()) < tol
+            out, ref = _attention_case(ops, [(60, 40)], 2, 1, 16, 8, 24, 5, boost=(None, far))
+            assert float((out - ref).abs().max()) < tol
+
+
+def test_attention_missing_page_is_reported(ops16):
+    from fastgen_b200.csrc.ops import KernelError
+    from fastgen_b200.engine.step import StepContext
+    ctx = StepContext(DEV)
+    ctx.host_seq_slot, ctx.host_seq_cached, ctx.host_seq_start = [0], [20], [0, 1]
+    ctx.pos = torch.tensor([20], dtype=torch.int32, device=DEV)
+    ctx.req = torch.tensor([0], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[0, -1, 2]], dtype=torch.int32, device=DEV)  # page of positions 8..15 is missing
+    kp = torch.zeros(3, 1, 8, 16, dtype=torch.bfloat16, device=DEV)
+    q = torch.zeros(1, 16, dtype=torch.bfloat16, device=DEV)
+    out = torch.empty_like(q)
+    ops16.attention(q, out, kp, kp, table, 8, ctx, 1, 1, 16, None, 0.25)
+    with pytest.raises(KernelError, match="block-table"):
+        ops16.check_status()
+
+
+# ---------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------
+def test_argmax_and_logprobs(ops32):
+    g = torch.Generator().manual_seed(1)
+    for vocab in (5, 331, 128256):
+        logits = torch.randn(7, vocab, generator=g).to(DEV)
+        logits[2, vocab // 2] = logits[2, vocab - 1] = 9.0  # a tie: the lowest index wins
+        out = torch.empty(7, dtype=torch.int32, device=DEV)
+        lp = torch.empty(7, dtype=torch.float32, device=DEV)
+        ops32.sample(logits, None, 1.0, 0, None, None, out, lp, None)
+        ref = logits.argmax(-1)
+        assert out[2] == vocab // 2
+        keep = [0, 1, 3, 4, 5, 6]
+        assert torch.equal(out[keep].long(), ref[keep])
+        ref_lp = torch.log_softmax(logits.double(), -1)[torch.arange(7), out.long()]
+        assert torch.allclose(lp.double(), ref_lp, atol=1e-4)
+
+
+@pytest.mark.parametrize("top_p", [1.0, 0.9, 0.5])
+def test_sampling_matches_inverse_cdf(ops32, top_p):
+    g = torch.Generator().manual_seed(2)
+    rows, vocab = 64, 1000
+    logits = (torch.randn(rows, vocab, generator=g) * 2).to(DEV)
+    temps = torch.full((rows,), 0.8, device=DEV)
+    keys = torch.arange(rows, dtype=torch.int64, device=DEV)
+    posn = torch.arange(100, 100 + rows, dtype=torch.int32, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * vocab, device=DEV)
+    ops32.sample(logits, temps, top_p, 1234, keys, posn, out, None, scratch)
+    u = ops32.sample_uniform(1234, keys, posn).double().cpu()
+    assert 0 <= u.min() and u.max() < 1
+    probs = pl.softmax_temperature(logits.cpu(), 0.8)
+    keep = pl.top_p_keep(probs, top_p) if top_p < 1 else torch.ones_like(probs, dtype=torch.bool)
+    kept = torch.where(keep, probs, torch.zeros_like(probs))
+    cdf = torch.cumsum(kept, -1)
+    exact = 0
+    for r in range(rows):
+        tok = int(out[r])
+        assert keep[r, tok], "a token outside the nucleus was drawn"
+        goal = u[r] * cdf[r, -1]
+        lo = cdf[r, tok] - kept[r, tok]
+        # the drawn token's interval contains u * mass, up to float32 rounding of the sums
+        assert lo - 1e-4 <= goal <= cdf[r, tok] + 1e-4
+        exact += int(torch.searchsorted(cdf[r], goal, right=True)) == tok
+    assert exact >= rows - 2
+    # the same keys give the same tokens whatever the batch; other keys give others
+    out2 = torch.empty(8, dtype=torch.int32, device=DEV)
+    ops32.sample(logits[8:16].contiguous(), temps[:8], top_p, 1234, keys[8:16].contiguous(),
+                 posn[8:16].contiguous(), out2, None, scratch)
+    assert torch.equal(out2, out[8:16])
+
+
+def test_sampling_distribution(ops32):
+    vocab, rows = 16, 4096
+    logits = torch.linspace(-2, 2, vocab).repeat(rows, 1).to(DEV)
+    temps = torch.ones(rows, device=DEV)
+    keys = torch.arange(rows, dtype=torch.int64, device=DEV)
+    posn = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops32.sample(logits, temps, 1.0, 99, keys, posn, out, None, torch.empty(rows * vocab, device=DEV))
+    freq = torch.bincount(out.long().cpu(), minlength=vocab).double() / rows
+    probs = torch.softmax(torch.linspace(-2, 2, vocab).double(), 0)
+    assert float((freq - probs).abs().max()) < 0.02
+    u = ops32.sample_uniform(99, keys, posn).cpu()
+    assert abs(float(u.mean()) - 0.5) < 0.02 and abs(float(u.var()) - 1 / 12) < 0.01
