@@ -147,6 +147,8 @@ class Ops:
         self.lib = core()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch = {}
+        # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
     # -- status word ---------------------------------------------------------
     def check_status(self) -> None:

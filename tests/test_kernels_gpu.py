@@ -95,9 +95,12 @@ def test_linear_bf16(ops16):
     x = torch.randn(9, 200, generator=g).to(DEV, torch.bfloat16)
     w = torch.randn(331, 200, generator=g).to(DEV, torch.bfloat16)
     ref = x.double() @ w.double().T
-    assert torch.allclose(ops16.linear(x, w).double(), ref, rtol=2e-2, atol=0.2)
+    # float32 accumulation, one rounding to bfloat16 at the end (half an ulp = 2^-9 relative)
+    err = (ops16.linear(x, w).double() - ref).abs()
+    assert bool((err <= ref.abs() * 2.0 ** -8 + 1e-2).all()), float(err.max())
     out32 = ops16.linear(x, w, out_dtype=torch.float32)
-    assert out32.dtype == torch.float32 and torch.allclose(out32.double(), ref, rtol=1e-3, atol=1e-2)
+    assert out32.dtype == torch.float32
+    assert torch.allclose(out32.double(), ref, rtol=1e-4, atol=1e-3), float((out32.double() - ref).abs().max())
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -132,12 +135,11 @@ def test_rope_kv_write(ops32, dtype, hq, hkv, hd, page):
     q = qkv[:, : hq * hd]; k = qkv[:, hq * hd : (hq + hkv) * hd]; v = qkv[:, (hq + hkv) * hd :]
     ops32.rope_kv_write(q, k, v, pos, req, freqs, kp, vp, table, page, hq, hkv, hd)
     ops32.check_status()
-    od = orig.double()
+    od = orig.double().cpu()
     rq = pl.apply_rope(od[:, : hq * hd].view(t, hq, hd), pos.cpu(), freqs.cpu()).view(t, -1)
     rk = pl.apply_rope(od[:, hq * hd : (hq + hkv) * hd].view(t, hkv, hd), pos.cpu(), freqs.cpu())
     tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
     assert torch.allclose(q[:22].double().cpu(), rq[:22].cpu(), **tol)
-    assert torch.equal(q[22], orig[22, : hq * hd]) or True  # padding: queries may be rotated, pages must not change
     written = torch.zeros(n_pages, page, dtype=torch.bool)
     for i in range(22):
         pg = int(table[int(req[i]), int(pos[i]) // page]); off = int(pos[i]) % page
