@@ -153,11 +153,13 @@ def run_ours(args) -> dict:
         engine.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])])
         engine.release("p")
 
-    for _ in range(3):
-        prefill_once()
-    pre_ms = min(event_ms(prefill_once, 5))
+    pre_ms = float("nan")
+    if not args.skip_prefill:
+        for _ in range(3):
+            prefill_once()
+        pre_ms = min(event_ms(prefill_once, 5))
     pre_flops = model_flops(cfg, n_layers, PREFILL_TOKENS, 1)
-    prefill = dict(value=round(PREFILL_TOKENS / pre_ms * 1e3, 1), tokens=PREFILL_TOKENS, ms=round(pre_ms, 3),
+    prefill = None if args.skip_prefill else dict(value=round(PREFILL_TOKENS / pre_ms * 1e3, 1), tokens=PREFILL_TOKENS, ms=round(pre_ms, 3),
                    frac=round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                    tflops=round(pre_flops / (pre_ms * 1e-3) / 1e12, 1), peak_tflops=pk["bf16_tflops"])
 
@@ -213,6 +215,9 @@ def run_ours(args) -> dict:
         return dict(ms_per_step=ms / steps, tok_s=batch * steps / ms * 1e3, launches=launches,
                     gbs=step_bytes / (ms / steps * 1e-3) / 1e9, clocks=clk, first=first_len, last=last_len)
 
+    if args.skip_decode:
+        print(json.dumps({"impl": "ours", "prefill": prefill, "note": "decode skipped"}))
+        sys.exit(0)
     clocks = ClockSampler()
     main = decode_run(args.batch, k, w, clocks)
     points = {}
@@ -226,23 +231,25 @@ def run_ours(args) -> dict:
     # ---- the same through the Python entry point: host tokens in, host tokens out ----
     del engine
     torch.cuda.empty_cache()
-    fg = Fastgen(GenArgs(use_sampling=False, max_batch=args.batch, max_seq=args.batch * (ctx_len + PAGE),
+    e2e = None
+    fg = None if args.skip_e2e else Fastgen(GenArgs(use_sampling=False, max_batch=args.batch, max_seq=args.batch * (ctx_len + PAGE),
                          max_gen=k + w, cache_block=PAGE, max_prefill=PREFILL_TOKENS,
                          num_cuda_graphs=args.batch), model, stop_tokens=[])
-    q = queue.Queue()
-    for i in range(args.batch):
-        q.put(Packet(thread_id=i, tokens=prompt(prompt_len)))
-    q.put(None)
-    n_out = sum(len(p.tokens) for p in fg.generate(q))
-    log = [s for s in fg.step_log if s["prompt_tokens"] == 0 and s["decode_tokens"] == args.batch]
-    tail = log[-k:] if len(log) > k else log[1:]
-    e2e_tokens = sum(s["decode_tokens"] for s in tail)
-    e2e_s = tail[-1]["t_end"] - tail[0]["t_start"]
-    e2e = dict(value=round(e2e_tokens / e2e_s, 1), unit="tokens/s",
-               h2d_bytes_per_step=int(sum(s["h2d_bytes"] for s in tail) / len(tail)),
-               d2h_bytes_per_step=int(sum(s["d2h_bytes"] for s in tail) / len(tail)),
-               steps=len(tail), generated=n_out)
-    fg.destroy()
+    if fg is not None:
+        q = queue.Queue()
+        for i in range(args.batch):
+            q.put(Packet(thread_id=i, tokens=prompt(prompt_len)))
+        q.put(None)
+        n_out = sum(len(p.tokens) for p in fg.generate(q))
+        log = [s for s in fg.step_log if s["prompt_tokens"] == 0 and s["decode_tokens"] == args.batch]
+        tail = log[-k:] if len(log) > k else log[1:]
+        e2e_tokens = sum(s["decode_tokens"] for s in tail)
+        e2e_s = tail[-1]["t_end"] - tail[0]["t_start"]
+        e2e = dict(value=round(e2e_tokens / e2e_s, 1), unit="tokens/s",
+                   h2d_bytes_per_step=int(sum(s["h2d_bytes"] for s in tail) / len(tail)),
+                   d2h_bytes_per_step=int(sum(s["d2h_bytes"] for s in tail) / len(tail)),
+                   steps=len(tail), generated=n_out)
+        fg.destroy()
 
     return {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (8B, bf16)",
@@ -287,6 +294,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--skip-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the run through the Python entry point")
+    ap.add_argument("--skip-decode", action="store_true", help="skip the decode measurement (profiling prefill)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

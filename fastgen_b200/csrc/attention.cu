@@ -145,7 +145,7 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         scale_log2, scratch, max_splits, status);
   FG_CHECK_LAUNCH("fg_attention_decode_bf16");
   dim3 cgrid(n_heads, n_seqs);
-  attention_combine_kernel<FG_HEAD_DIM><<<cgrid, FG_HEAD_DIM < 128 ? FG_HEAD_DIM : 128, 0, stream>>>(
+  attention_combine_kernel<FG_HEAD_DIM><<<cgrid, 128, 0, stream>>>(
       scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, status);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;

@@ -84,21 +84,22 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bflo
                                              int rows, int k_begin, int k_end, int tid, int nthreads,
                                              int* status) {
   constexpr int CH = HD / 8;  // 16-byte chunks per row
-  for (int i = tid; i < rows * CH; i += nthreads) {
-    const int r = i / CH, c = i - r * CH;
-    const int j = k0 + r;
-    const __nv_bfloat16* src = pages;
-    bool ok = j >= k_begin && j < k_end;
-    if (ok) {
-      const int logical = j / page_size;
-      const int page = logical < table_width ? table_row[logical] : -1;
-      ok = page >= 0 && page < n_pages;
-      if (!ok && c == 0 && status) atomicOr(status, FG_STATUS_BAD_PAGE);
-      if (ok)
-        src = pages + (((size_t)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD + c * 8;
-    }
-    cp_async_16(dst + r * Tile<HD>::LD + c * 8, src, ok);
+  // nthreads is a multiple of rows: a row is shared by nthreads/rows threads, so
+  // the page look-up (a division) happens once per thread
+  const int tpr = nthreads / rows;
+  const int r = tid / tpr, part = tid - r * tpr;
+  const int j = k0 + r;
+  const __nv_bfloat16* src = pages;
+  bool ok = j >= k_begin && j < k_end;
+  if (ok) {
+    const int logical = j / page_size;
+    const int page = logical < table_width ? table_row[logical] : -1;
+    ok = page >= 0 && page < n_pages;
+    if (!ok && part == 0 && status) atomicOr(status, FG_STATUS_BAD_PAGE);
+    if (ok) src = pages + (((size_t)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
   }
+  __nv_bfloat16* drow = dst + r * Tile<HD>::LD;
+  for (int c = part; c < CH; c += tpr) cp_async_16(drow + c * 8, ok ? src + c * 8 : pages, ok);
 }
 
 // S[16 x NK*8] += Q[16 x HD] K^T for one warp; K rows start at `ks`.
@@ -333,13 +334,51 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 // ---------------------------------------------------------------------------------
 // decode: split over key positions, then combine
 // ---------------------------------------------------------------------------------
+// Bulk asynchronous copies (the TMA engine, untiled form) tracked by an mbarrier.
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::);
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t* bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// 16-byte aligned source and destination, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, int bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// Bounded wait: gives up after ~2^22 polls, records it and lets the block finish
+// (its copies have either landed or the data is reported as unusable).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, int* status) {
+  for (int it = 0; it < (1 << 22); ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  if (status) atomicOr(status, FG_STATUS_WAIT_TIMEOUT);
+  return false;
+}
+
 template <int HD>
 constexpr size_t decode_smem_bytes() {
-  // K and V of the split, the padded queries; the merge buffers reuse K's space
+  // K and V of the split and the padded queries; the merge buffers reuse K's space
   return sizeof(__nv_bfloat16) * Tile<HD>::LD * (2 * DECODE_SPLIT + DECODE_ROWS);
 }
 
-// scratch layout per (token, split, head): HD floats of output, then (max, sum)
+// scratch layout per (token, head, split): HD floats of output, then (max, sum)
 template <int HD>
 __host__ __device__ constexpr int part_stride() { return HD + 2; }
 
@@ -352,12 +391,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const int* __restrict__ seq_tok, int n_heads, int n_kv_heads, int group,
                         int window, float scale_log2, float* __restrict__ scratch, int max_splits,
                         int* status) {
+  static_assert(THREADS == DECODE_SPLIT, "one thread per key position of the split");
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = 4;  // 32 key positions per warp
+  constexpr int ROW_BYTES = HD * 2;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Vs = Ks + DECODE_SPLIT * LD;
   __nv_bfloat16* Qs = Vs + DECODE_SPLIT * LD;
+  __shared__ __align__(8) uint64_t bars[2];  // K landed, V landed
 
   const int split = blockIdx.x, g = blockIdx.y, seq = blockIdx.z;
   const int b = seq_req[seq];
@@ -370,36 +412,64 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   if (k0 + DECODE_SPLIT <= k_begin) return;  // wholly before the window
   const int k_end = p + 1;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int* table_row = block_table + (size_t)b * table_width;
 
-  load_kv_tile<HD>(Ks, k_pages, table_row, table_width, page_size, n_pages, n_kv_heads, g, k0, DECODE_SPLIT,
-                   k_begin, k_end, tid, THREADS, status);
+  if (tid == 0) {
+    mbar_init(&bars[0], THREADS);
+    mbar_init(&bars[1], THREADS);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // thread t brings key row k0 + t and value row k0 + t: one bulk copy each
+  {
+    const int j = k0 + tid;
+    bool ok = j >= k_begin && j < k_end;
+    size_t off = 0;
+    if (ok) {
+      const int logical = j / page_size;
+      const int page = logical < table_width ? block_table[(size_t)b * table_width + logical] : -1;
+      ok = page >= 0 && page < n_pages;
+      if (!ok && status) atomicOr(status, FG_STATUS_BAD_PAGE);
+      off = (((size_t)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
+    }
+    if (ok) {
+      mbar_arrive_expect(&bars[0], ROW_BYTES);
+      bulk_copy_g2s(Ks + tid * LD, k_pages + off, ROW_BYTES, &bars[0]);
+      mbar_arrive_expect(&bars[1], ROW_BYTES);
+      bulk_copy_g2s(Vs + tid * LD, v_pages + off, ROW_BYTES, &bars[1]);
+    } else {
+      // rows outside the request: zeros (a masked probability times garbage could be NaN)
+      uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
+        *reinterpret_cast<uint4*>(Ks + tid * LD + c * 8) = z;
+        *reinterpret_cast<uint4*>(Vs + tid * LD + c * 8) = z;
+      }
+      mbar_arrive(&bars[0]);
+      mbar_arrive(&bars[1]);
+    }
+  }
+
   constexpr int CH = HD / 8;
   for (int sub = 0; sub * DECODE_ROWS < group; ++sub) {
-    // (groups wider than 16 heads are walked in slices of 16; K and V stay in place)
+    // groups wider than 16 heads are walked in slices of 16; K and V stay in place
+    const int rows_here = min(DECODE_ROWS, group - sub * DECODE_ROWS);
     if (sub > 0) __syncthreads();
     for (int i = tid; i < DECODE_ROWS * CH; i += THREADS) {
       const int r = i / CH, c = i - r * CH;
-      const int head = sub * DECODE_ROWS + r;
-      const bool ok = head < group;
-      const __nv_bfloat16* src = ok ? q + (size_t)tok * q_stride + (g * group + head) * HD + c * 8 : q;
-      cp_async_16(Qs + r * LD + c * 8, src, ok);
-    }
-    cp_async_commit();
-    if (sub == 0) {
-      load_kv_tile<HD>(Vs, v_pages, table_row, table_width, page_size, n_pages, n_kv_heads, g, k0,
-                       DECODE_SPLIT, k_begin, k_end, tid, THREADS, status);
-      cp_async_commit();
-      cp_async_wait<1>();  // K and Q
-    } else {
-      cp_async_wait<0>();
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows_here)
+        v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride +
+                                            (g * group + sub * DECODE_ROWS + r) * HD + c * 8);
+      *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
     }
     __syncthreads();
-
     uint32_t qf[HD / 16][4];
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk)
       ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
+
+    if (sub == 0) mbar_wait(&bars[0], 0, status);
     float s[NT][4];
     qk_product<HD, NT>(s, qf, Ks + warp * 32 * LD, lane);
 #pragma unroll
@@ -415,15 +485,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     softmax_step<HD, NT>(s, o, m, l);
-    cp_async_wait<0>();  // V
-    __syncthreads();
+    if (sub == 0) mbar_wait(&bars[1], 0, status);
     pv_product<HD, NT>(o, s, Vs + warp * 32 * LD, lane);
 
-    // merge the 4 warps: max and sum per row, then the outputs, through shared memory
-    __syncthreads();  // K is no longer needed: its space holds the merge buffers
-    float* wm = reinterpret_cast<float*>(Ks);         // [4][16]
-    float* wl = wm + 4 * DECODE_ROWS;                   // [4][16]
-    float* wo = wl + 4 * DECODE_ROWS;                   // [4][16][HD]
+    // merge the 4 warps through shared memory (only the rows that hold heads)
+    float* wm = reinterpret_cast<float*>(Qs);           // [4][16] max, then [4][16] sum: fits the Q tile
+    float* wl = wm + 4 * DECODE_ROWS;
+    __syncthreads();                                    // all warps are done with Q and K
+    float* wo = reinterpret_cast<float*>(Ks);           // [4][rows][HD]
     const int r0 = lane >> 2;
     if ((lane & 3) == 0) {
       wm[warp * DECODE_ROWS + r0] = m[0];
@@ -434,14 +503,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
       const int d = nt * 8 + 2 * (lane & 3);
-      float* dst = wo + (warp * DECODE_ROWS + r0) * HD + d;
-      dst[0] = o[nt][0];
-      dst[1] = o[nt][1];
-      dst[8 * HD] = o[nt][2];
-      dst[8 * HD + 1] = o[nt][3];
+      if (r0 < rows_here)
+        *reinterpret_cast<float2*>(wo + (warp * DECODE_ROWS + r0) * HD + d) = make_float2(o[nt][0], o[nt][1]);
+      if (r0 + 8 < rows_here)
+        *reinterpret_cast<float2*>(wo + (warp * DECODE_ROWS + r0 + 8) * HD + d) = make_float2(o[nt][2], o[nt][3]);
     }
     __syncthreads();
-    const int rows_here = min(DECODE_ROWS, group - sub * DECODE_ROWS);
     for (int i = tid; i < rows_here * HD; i += THREADS) {
       const int r = i / HD, d = i - r * HD;
       float mm = -INFINITY;
@@ -456,34 +523,41 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         ll += f * wl[w * DECODE_ROWS + r];
       }
       const int head = g * group + sub * DECODE_ROWS + r;
-      float* dst = scratch + (((size_t)seq * max_splits + split) * n_heads + head) * part_stride<HD>();
+      float* dst = scratch + (((size_t)seq * n_heads + head) * max_splits + split) * part_stride<HD>();
       dst[d] = acc;
       if (d == 0) {
         dst[HD] = mm;
         dst[HD + 1] = ll;
       }
     }
-    // K's space is reused: a further slice of heads must reload it
     if ((sub + 1) * DECODE_ROWS < group) {
+      // K's space was used for the merge: bring the keys back for the next slice of heads
       __syncthreads();
-      load_kv_tile<HD>(Ks, k_pages, table_row, table_width, page_size, n_pages, n_kv_heads, g, k0,
-                       DECODE_SPLIT, k_begin, k_end, tid, THREADS, status);
+      load_kv_tile<HD>(Ks, k_pages, block_table + (size_t)b * table_width, table_width, page_size, n_pages,
+                       n_kv_heads, g, k0, DECODE_SPLIT, k_begin, k_end, tid, THREADS, status);
+      cp_async_commit();
+      cp_async_wait<0>();
     }
   }
 }
 
 // out[token, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m) over the
-// request's splits, in ascending split order.
+// request's splits, in ascending split order.  One block per (head, token).
 template <int HD>
-__global__ void attention_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out,
-                                         int out_stride, const int* __restrict__ pos,
-                                         const int* __restrict__ seq_req, const int* __restrict__ seq_tok,
-                                         int n_heads, int window, int max_splits, int* status) {
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int out_stride,
+                         const int* __restrict__ pos, const int* __restrict__ seq_req,
+                         const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
+                         int* status) {
+  constexpr int CHUNK = 128;  // splits whose weights are staged at a time
+  __shared__ float w_s[CHUNK];
+  __shared__ float red[4];
   const int seq = blockIdx.y, head = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok = seq_tok[seq];
   __nv_bfloat16* dst = out + (size_t)tok * out_stride + head * HD;
   if (seq_req[seq] < 0) {
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) dst[d] = __float2bfloat16_rn(0.f);
+    for (int d = tid; d < HD; d += blockDim.x) dst[d] = __float2bfloat16_rn(0.f);
     return;
   }
   const int p = pos[tok];
@@ -491,26 +565,48 @@ __global__ void attention_combine_kernel(const float* __restrict__ scratch, __nv
   int s_hi = p / DECODE_SPLIT;  // inclusive
   if (s_hi >= max_splits) {
     // the launch was sized for shorter requests: report instead of reading past the scratch
-    if (threadIdx.x == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
+    if (tid == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
     s_hi = max_splits - 1;
   }
-  const float* base = scratch + ((size_t)seq * max_splits * n_heads + head) * part_stride<HD>();
-  const size_t step = (size_t)n_heads * part_stride<HD>();
+  const float* base = scratch + ((size_t)seq * n_heads + head) * max_splits * part_stride<HD>();
+  constexpr int PS = part_stride<HD>();
+  // the overall maximum
   float mm = -INFINITY;
-  for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, base[s * step + HD]);
+  for (int s = s_lo + tid; s <= s_hi; s += blockDim.x) mm = fmaxf(mm, base[(size_t)s * PS + HD]);
+  mm = warp_max(mm);
+  if (lane == 0) red[warp] = mm;
+  __syncthreads();
+  mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  float acc[(HD + 127) / 128];
+#pragma unroll
+  for (int i = 0; i < (HD + 127) / 128; ++i) acc[i] = 0.f;
   float ll = 0.f;
-  for (int s = s_lo; s <= s_hi; ++s) {
-    const float ms = base[s * step + HD];
-    if (ms != -INFINITY) ll += base[s * step + HD + 1] * exp2f(ms - mm);
+  for (int c0 = s_lo; c0 <= s_hi; c0 += CHUNK) {
+    const int n = min(CHUNK, s_hi - c0 + 1);
+    __syncthreads();
+    if (tid < n) {
+      const float ms = base[(size_t)(c0 + tid) * PS + HD];
+      w_s[tid] = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+    }
+    __syncthreads();
+    // every thread accumulates the sum in the same ascending order
+    for (int s = 0; s < n; ++s) ll += w_s[s] * base[(size_t)(c0 + s) * PS + HD + 1];
+#pragma unroll
+    for (int i = 0; i < (HD + 127) / 128; ++i) {
+      const int d = tid + i * 128;
+      if (d < HD) {
+        float a = acc[i];
+#pragma unroll 8
+        for (int s = 0; s < n; ++s) a += w_s[s] * base[(size_t)(c0 + s) * PS + d];
+        acc[i] = a;
+      }
+    }
   }
   const float inv = ll > 0.f ? 1.f / ll : 0.f;
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-      const float ms = base[s * step + HD];
-      if (ms != -INFINITY) acc += base[s * step + d] * exp2f(ms - mm);
-    }
-    dst[d] = __float2bfloat16_rn(acc * inv);
+#pragma unroll
+  for (int i = 0; i < (HD + 127) / 128; ++i) {
+    const int d = tid + i * 128;
+    if (d < HD) dst[d] = __float2bfloat16_rn(acc[i] * inv);
   }
 }
 

@@ -40,6 +40,7 @@ CORE_SOURCES = [
     "rope_kv.cu",
     "silu_gate.cu",
     "gemm_f32.cu",
+    "gemm_skinny.cu",
     "sampling.cu",
 ]
 

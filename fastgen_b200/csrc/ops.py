@@ -45,6 +45,7 @@ _CORE_SIGNATURES = {
     "fg_silu_gate": [_P, _P, _I, _I, _I, _P],
     "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
+    "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
     "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
 }
@@ -56,6 +57,7 @@ _ATTN_SIGNATURES = {
                                  ctypes.c_longlong, _I, _P, _P],
 }
 
+SKINNY_MAX_M = 32     # most tokens the weight-streaming product takes
 SIMT_ROWS = 16       # query rows per block of the float32 attention kernel
 PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
 DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kernel
@@ -214,6 +216,16 @@ class Ops:
             return out
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
         want = out.dtype if out is not None else (out_dtype or torch.bfloat16)
+        if (m <= SKINNY_MAX_M and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            # few tokens: this package's weight-streaming kernel
+            if out is None:
+                out = torch.empty((m, n), dtype=want, device=x.device)
+            assert out.stride(1) == 1
+            _check(self.lib, self.lib.fg_gemm_skinny_bf16(
+                _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out.dtype),
+                m, n, k, _stream()))
+            return out
         if want == torch.bfloat16:
             return torch.mm(x, w.t(), out=out) if out is not None else torch.mm(x, w.t())
         # float32 result of a bfloat16 product (logits)

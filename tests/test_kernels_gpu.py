@@ -103,6 +103,28 @@ def test_linear_bf16(ops16):
     assert torch.allclose(out32.double(), ref, rtol=1e-4, atol=1e-3), float((out32.double() - ref).abs().max())
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(320, 192), (331, 200), (4096, 4096), (1000, 14336), (17, 72), (64, 8)])
+def test_gemm_skinny(ops16, m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(DEV, torch.bfloat16)
+    ref = x.double() @ w.double().T
+    out32 = ops16.linear(x, w, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    assert torch.allclose(out32.double(), ref, rtol=1e-4, atol=2e-4), float((out32.double() - ref).abs().max())
+    out16 = ops16.linear(x, w)
+    err = (out16.double() - ref).abs()
+    assert bool((err <= ref.abs() * 2.0 ** -8 + 1e-3).all()), float(err.max())
+    # a row does not depend on the other rows of the batch: bitwise
+    one = ops16.linear(x[m - 1 : m], w, out_dtype=torch.float32)
+    assert torch.equal(one[0], out32[m - 1])
+    # a column slice of a wider buffer as input, a wider buffer as output
+    wide = torch.zeros(m, k + 16, dtype=torch.bfloat16, device=DEV)
+    wide[:, 8 : 8 + k] = x
+    assert torch.equal(ops16.linear(wide[:, 8 : 8 + k], w, out_dtype=torch.float32), out32)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("ffn", [176, 331, 14336])
 def test_silu_gate(ops32, dtype, ffn):
