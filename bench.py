@@ -172,9 +172,18 @@ def run_ours(args) -> dict:
         for rid in ids:
             engine.admit(rid)
         for rid in ids:  # fill the cache: the prompt in portions of 2,048
+            if args.fast_fill:
+                r = engine.cache.get(rid)
+                engine.cache.reserve(r, prompt_len)
+                engine.cache.advance(r, prompt_len)
+                continue
             p = prompt(prompt_len)
             for s in range(0, prompt_len, PREFILL_TOKENS):
                 engine.step([StepEntry(rid, p[s:s + PREFILL_TOKENS], [])])
+        if args.fast_fill:
+            for grp in engine.cache.groups:
+                grp.k_pages.normal_(0.0, 1.0)
+                grp.v_pages.normal_(0.0, 1.0)
         reqs = [engine.cache.get(rid) for rid in ids]
         slots = [r.slot for r in reqs]
         tokens = torch.randint(0, vocab, (batch,), generator=gen).to(dev, torch.int32)
@@ -297,6 +306,8 @@ def main() -> int:
     ap.add_argument("--skip-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the run through the Python entry point")
     ap.add_argument("--skip-decode", action="store_true", help="skip the decode measurement (profiling prefill)")
+    ap.add_argument("--fast-fill", action="store_true",
+                    help="profiling only: fill the cache pages with random values instead of prefilling the prompts")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

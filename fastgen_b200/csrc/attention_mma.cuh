@@ -74,32 +74,41 @@ struct Tile {
   static constexpr int LD = HD + 8;
 };
 
-// Bring `rows` key (or value) rows, positions k0 .. k0+rows-1 of request `b`,
-// into shared memory through the block table.  Rows beyond `k_end` (exclusive),
-// below `k_begin`, or without a page are zero-filled.
+// Offsets (in elements, -1 = no such row) of the key/value rows k0 .. k0+rows-1 of
+// a request in its pools: one page look-up (a division) per row, done by `rows`
+// threads.  Rows outside [k_begin, k_end) or without a page get -1.
 template <int HD>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pages,
-                                             const int* __restrict__ table_row, int table_width,
-                                             int page_size, int n_pages, int n_kv_heads, int g, int k0,
-                                             int rows, int k_begin, int k_end, int tid, int nthreads,
-                                             int* status) {
-  constexpr int CH = HD / 8;  // 16-byte chunks per row
-  // nthreads is a multiple of rows: a row is shared by nthreads/rows threads, so
-  // the page look-up (a division) happens once per thread
-  const int tpr = nthreads / rows;
-  const int r = tid / tpr, part = tid - r * tpr;
-  const int j = k0 + r;
-  const __nv_bfloat16* src = pages;
-  bool ok = j >= k_begin && j < k_end;
-  if (ok) {
-    const int logical = j / page_size;
-    const int page = logical < table_width ? table_row[logical] : -1;
-    ok = page >= 0 && page < n_pages;
-    if (!ok && part == 0 && status) atomicOr(status, FG_STATUS_BAD_PAGE);
-    if (ok) src = pages + (((size_t)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
+__device__ __forceinline__ void kv_row_offsets(long long* row_off, const int* __restrict__ table_row,
+                                               int table_width, int page_size, int n_pages, int n_kv_heads,
+                                               int g, int k0, int rows, int k_begin, int k_end, int tid,
+                                               int* status) {
+  if (tid < rows) {
+    const int j = k0 + tid;
+    long long off = -1;
+    if (j >= k_begin && j < k_end) {
+      const int logical = j / page_size;
+      const int page = logical < table_width ? table_row[logical] : -1;
+      if (page >= 0 && page < n_pages)
+        off = (((long long)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
+      else if (status)
+        atomicOr(status, FG_STATUS_BAD_PAGE);
+    }
+    row_off[tid] = off;
   }
-  __nv_bfloat16* drow = dst + r * Tile<HD>::LD;
-  for (int c = part; c < CH; c += tpr) cp_async_16(drow + c * 8, ok ? src + c * 8 : pages, ok);
+}
+
+// Bring `rows` rows into shared memory with 16-byte asynchronous copies;
+// consecutive threads take consecutive pieces of a row.  Rows with offset -1 are
+// zero-filled.
+template <int HD>
+__device__ __forceinline__ void load_kv_rows(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pages,
+                                             const long long* row_off, int rows, int tid, int nthreads) {
+  constexpr int CH = HD / 8;  // 16-byte pieces per row
+  for (int i = tid; i < rows * CH; i += nthreads) {
+    const int r = i / CH, c = i - r * CH;
+    const long long off = row_off[r];
+    cp_async_16(dst + r * Tile<HD>::LD + c * 8, off >= 0 ? pages + off + c * 8 : pages, off >= 0);
+  }
 }
 
 // S[16 x NK*8] += Q[16 x HD] K^T for one warp; K rows start at `ks`.
@@ -213,6 +222,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   __nv_bfloat16* Ks = Qs + PREFILL_ROWS * LD;            // 2 stages
   __nv_bfloat16* Vs = Ks + 2 * PREFILL_KEYS * LD;        // 2 stages
   __shared__ int row_pos[PREFILL_ROWS];
+  __shared__ long long row_off[2][PREFILL_KEYS];
 
   const int tile = blockIdx.x, g = blockIdx.y, sub = blockIdx.z;
   const int b = tile_req[tile];
@@ -257,15 +267,21 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const int* table_row = block_table + (size_t)b * table_width;
   const int n_tiles = (k_end - k_lo + PREFILL_KEYS - 1) / PREFILL_KEYS;
 
+  // offsets of tile t's rows are computed one tile ahead of its copies
+  auto offsets = [&](int t) {
+    kv_row_offsets<HD>(row_off[t & 1], table_row, table_width, page_size, n_pages, n_kv_heads, g,
+                       k_lo + t * PREFILL_KEYS, PREFILL_KEYS, k_begin, k_end, tid, status);
+  };
   auto issue = [&](int t) {
     const int stage = t & 1;
-    load_kv_tile<HD>(Ks + stage * PREFILL_KEYS * LD, k_pages, table_row, table_width, page_size, n_pages,
-                     n_kv_heads, g, k_lo + t * PREFILL_KEYS, PREFILL_KEYS, k_begin, k_end, tid, THREADS, status);
-    load_kv_tile<HD>(Vs + stage * PREFILL_KEYS * LD, v_pages, table_row, table_width, page_size, n_pages,
-                     n_kv_heads, g, k_lo + t * PREFILL_KEYS, PREFILL_KEYS, k_begin, k_end, tid, THREADS, status);
+    load_kv_rows<HD>(Ks + stage * PREFILL_KEYS * LD, k_pages, row_off[stage], PREFILL_KEYS, tid, THREADS);
+    load_kv_rows<HD>(Vs + stage * PREFILL_KEYS * LD, v_pages, row_off[stage], PREFILL_KEYS, tid, THREADS);
     cp_async_commit();
   };
+  offsets(0);
+  __syncthreads();
   issue(0);
+  if (n_tiles > 1) offsets(1);
 
   // the warp's 16 rows; this thread's two rows
   const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
@@ -293,6 +309,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       cp_async_wait<0>();
     }
     __syncthreads();
+    // tile t's rows have landed and its offsets are no longer needed
+    if (t + 2 < n_tiles) offsets(t + 2);
     const int k0 = k_lo + t * PREFILL_KEYS;
     if (k0 <= warp_max) {
       const __nv_bfloat16* ks = Ks + (t & 1) * PREFILL_KEYS * LD;
@@ -391,15 +409,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const int* __restrict__ seq_tok, int n_heads, int n_kv_heads, int group,
                         int window, float scale_log2, float* __restrict__ scratch, int max_splits,
                         int* status) {
-  static_assert(THREADS == DECODE_SPLIT, "one thread per key position of the split");
+  static_assert(THREADS >= DECODE_SPLIT, "one thread per key position computes its row offset");
   constexpr int LD = Tile<HD>::LD;
   constexpr int NT = 4;  // 32 key positions per warp
-  constexpr int ROW_BYTES = HD * 2;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Vs = Ks + DECODE_SPLIT * LD;
   __nv_bfloat16* Qs = Vs + DECODE_SPLIT * LD;
-  __shared__ __align__(8) uint64_t bars[2];  // K landed, V landed
+  __shared__ long long row_off[DECODE_SPLIT];
 
   const int split = blockIdx.x, g = blockIdx.y, seq = blockIdx.z;
   const int b = seq_req[seq];
@@ -413,42 +430,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   const int k_end = p + 1;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  if (tid == 0) {
-    mbar_init(&bars[0], THREADS);
-    mbar_init(&bars[1], THREADS);
-    mbar_fence_init();
-  }
+  kv_row_offsets<HD>(row_off, block_table + (size_t)b * table_width, table_width, page_size, n_pages,
+                     n_kv_heads, g, k0, DECODE_SPLIT, k_begin, k_end, tid, status);
   __syncthreads();
-
-  // thread t brings key row k0 + t and value row k0 + t: one bulk copy each
-  {
-    const int j = k0 + tid;
-    bool ok = j >= k_begin && j < k_end;
-    size_t off = 0;
-    if (ok) {
-      const int logical = j / page_size;
-      const int page = logical < table_width ? block_table[(size_t)b * table_width + logical] : -1;
-      ok = page >= 0 && page < n_pages;
-      if (!ok && status) atomicOr(status, FG_STATUS_BAD_PAGE);
-      off = (((size_t)page * n_kv_heads + g) * page_size + (j - logical * page_size)) * HD;
-    }
-    if (ok) {
-      mbar_arrive_expect(&bars[0], ROW_BYTES);
-      bulk_copy_g2s(Ks + tid * LD, k_pages + off, ROW_BYTES, &bars[0]);
-      mbar_arrive_expect(&bars[1], ROW_BYTES);
-      bulk_copy_g2s(Vs + tid * LD, v_pages + off, ROW_BYTES, &bars[1]);
-    } else {
-      // rows outside the request: zeros (a masked probability times garbage could be NaN)
-      uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        *reinterpret_cast<uint4*>(Ks + tid * LD + c * 8) = z;
-        *reinterpret_cast<uint4*>(Vs + tid * LD + c * 8) = z;
-      }
-      mbar_arrive(&bars[0]);
-      mbar_arrive(&bars[1]);
-    }
-  }
+  load_kv_rows<HD>(Ks, k_pages, row_off, DECODE_SPLIT, tid, THREADS);
+  cp_async_commit();
+  load_kv_rows<HD>(Vs, v_pages, row_off, DECODE_SPLIT, tid, THREADS);
+  cp_async_commit();
 
   constexpr int CH = HD / 8;
   for (int sub = 0; sub * DECODE_ROWS < group; ++sub) {
@@ -469,7 +457,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int kk = 0; kk < HD / 16; ++kk)
       ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
 
-    if (sub == 0) mbar_wait(&bars[0], 0, status);
+    if (sub == 0) {
+      cp_async_wait<1>();  // keys
+      __syncthreads();
+    }
     float s[NT][4];
     qk_product<HD, NT>(s, qf, Ks + warp * 32 * LD, lane);
 #pragma unroll
@@ -485,7 +476,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     softmax_step<HD, NT>(s, o, m, l);
-    if (sub == 0) mbar_wait(&bars[1], 0, status);
+    if (sub == 0) {
+      cp_async_wait<0>();  // values
+      __syncthreads();
+    }
     pv_product<HD, NT>(o, s, Vs + warp * 32 * LD, lane);
 
     // merge the 4 warps through shared memory (only the rows that hold heads)
@@ -533,8 +527,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if ((sub + 1) * DECODE_ROWS < group) {
       // K's space was used for the merge: bring the keys back for the next slice of heads
       __syncthreads();
-      load_kv_tile<HD>(Ks, k_pages, block_table + (size_t)b * table_width, table_width, page_size, n_pages,
-                       n_kv_heads, g, k0, DECODE_SPLIT, k_begin, k_end, tid, THREADS, status);
+      load_kv_rows<HD>(Ks, k_pages, row_off, DECODE_SPLIT, tid, THREADS);
       cp_async_commit();
       cp_async_wait<0>();
     }

@@ -18,7 +18,6 @@
 
 namespace {
 
-constexpr int WARPS = 8;
 constexpr int ROWS = 16;   // rows of W per block
 constexpr int CHUNK = 64;  // k elements per warp step
 
@@ -45,7 +44,7 @@ __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, typename TO>
+template <int NT, typename TO, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
                    TO* __restrict__ y, int ldy, int M, int N, int K) {
@@ -141,12 +140,23 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int
   const int grid = (N + ROWS - 1) / ROWS;
   const auto* xp = (const __nv_bfloat16*)x;
   const auto* wp = (const __nv_bfloat16*)w;
+  // Few blocks (a small N): 16 warps a block, so that enough loads are in flight
+  // on every SM; the split of K only depends on N and K, never on the batch.
+  const bool wide = grid < 4 * 148 && K >= 16 * CHUNK;
+#define FG_SKINNY(NT)                                                                                       \
+  do {                                                                                                      \
+    if (wide)                                                                                               \
+      gemm_skinny_kernel<NT, TO, 16><<<grid, 16 * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K); \
+    else                                                                                                    \
+      gemm_skinny_kernel<NT, TO, 8><<<grid, 8 * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K);   \
+  } while (0)
   if (M <= 8)
-    gemm_skinny_kernel<1, TO><<<grid, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K);
+    FG_SKINNY(1);
   else if (M <= 16)
-    gemm_skinny_kernel<2, TO><<<grid, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K);
+    FG_SKINNY(2);
   else
-    gemm_skinny_kernel<4, TO><<<grid, WARPS * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K);
+    FG_SKINNY(4);
+#undef FG_SKINNY
   return 0;
 }
 
