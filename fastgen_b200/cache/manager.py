@@ -90,6 +90,7 @@ class CacheGroup:
     k_pages: Optional[torch.Tensor] = None  # [len(entries), n_pages, Hkv, page, hd]
     v_pages: Optional[torch.Tensor] = None
     device_table: Optional[torch.Tensor] = None  # [n_slots, table_width] int32
+    tensor_maps: Optional[tuple] = None  # made by the kernels' side for pools it can tile
     dirty: List[Tuple[int, int, int]] = field(default_factory=list)  # (slot, col, page)
 
     def first_needed_page(self, length: int) -> int:
@@ -113,6 +114,8 @@ class LayerMemory:
     page_size: int = 0
     writes: bool = True  # False: the run reads the cache another run writes
     state: Optional[torch.Tensor] = None  # [n_slots, *state_shape] float32
+    tensor_maps: Optional[tuple] = None  # TMA descriptors of the group's (key, value) pools
+    layer_index: int = 0  # this run's index within the group's pools
 
 
 class RequestCache:
@@ -148,6 +151,7 @@ class CacheManager:
         max_length: int,
         dtype: torch.dtype = torch.float32,
         device=None,
+        tensor_map_factory=None,
     ) -> None:
         if page_size <= 0:
             raise ValueError(f"page size must be positive, got {page_size}")
@@ -214,6 +218,8 @@ class CacheManager:
                 grp.device_table = torch.full(
                     (max_requests, grp.table_width), -1, dtype=torch.int32, device=device
                 )
+                if tensor_map_factory is not None:
+                    grp.tensor_maps = tensor_map_factory(grp.k_pages, grp.v_pages, page_size)
             for e, st in enumerate(self.state_specs):
                 if st is not None:
                     self.states[e] = torch.zeros(
@@ -360,6 +366,8 @@ class CacheManager:
                 mem.k_pages = grp.k_pages[i]
                 mem.v_pages = grp.v_pages[i]
                 mem.block_table = grp.device_table
+                mem.tensor_maps = grp.tensor_maps
+                mem.layer_index = i
         return mem
 
     # -- invariants (used by tests) --------------------------------------------------

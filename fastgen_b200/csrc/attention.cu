@@ -1,6 +1,8 @@
 // Attention entry points for one head size, fixed at compile time by
 // -DFG_HEAD_DIM=<multiple of 16>.  The builder compiles one library per head
 // size a model needs.
+#include <string.h>
+
 #include "attention_simt.cuh"
 
 #ifndef FG_HEAD_DIM
@@ -150,3 +152,62 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// single tokens with tiled TMA loads (head sizes that are multiples of 64)
+// ---------------------------------------------------------------------------------
+#if FG_HEAD_DIM % 64 == 0
+#include "attention_tma.cuh"
+
+extern "C" int fg_attention_decode_tma_supported() { return 1; }
+
+// As fg_attention_decode_bf16, with the pools given as tensor maps (128 bytes each,
+// on the host, made by fg_make_kv_tensor_map) and the layer's index in the pool.
+extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                            const void* k_map, const void* v_map, int layer,
+                                            const int* block_table, int table_width, int page_size,
+                                            int n_pages, const int* pos, const int* seq_req,
+                                            const int* seq_tok, int n_seqs, int n_heads, int n_kv_heads,
+                                            int head_dim, int window, float scale, float* scratch,
+                                            long long scratch_floats, int max_splits, int* status,
+                                            cudaStream_t stream) {
+  using namespace fg_tma;
+  if (n_seqs == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_tma_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535 && n_seqs <= 65535,
+               "fg_attention_decode_tma_bf16: %d heads over %d kv heads, %d sequences", n_heads, n_kv_heads, n_seqs);
+  const int group = n_heads / n_kv_heads;
+  FG_CHECK_ARG(group <= DECODE_ROWS, "fg_attention_decode_tma_bf16: groups of %d heads are not supported", group);
+  FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
+               "fg_attention_decode_tma_bf16: pages of %d slots are not supported", page_size);
+  FG_CHECK_ARG(max_splits > 0 && scratch != nullptr &&
+                   scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads),
+               "fg_attention_decode_tma_bf16: scratch of %lld floats is too small", scratch_floats);
+  FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
+               "fg_attention_decode_tma_bf16: queries must be 16-byte aligned with a row stride multiple of 8");
+  CUtensorMap km, vm;
+  memcpy(&km, k_map, sizeof(CUtensorMap));
+  memcpy(&vm, v_map, sizeof(CUtensorMap));
+  constexpr size_t smem = decode_tma_smem_bytes<FG_HEAD_DIM>();
+  auto kern = attention_decode_tma_kernel<FG_HEAD_DIM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  dim3 grid(max_splits, n_kv_heads, n_seqs);
+  kern<<<grid, THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, block_table,
+                                        table_width, page_size, n_pages, pos, seq_req, seq_tok, n_heads, group,
+                                        window, scale * 1.4426950408889634f, scratch, max_splits, status);
+  FG_CHECK_LAUNCH("fg_attention_decode_tma_bf16");
+  dim3 cgrid(n_heads, n_seqs);
+  fg_mma::attention_combine_kernel<FG_HEAD_DIM><<<cgrid, 128, 0, stream>>>(
+      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, status);
+  FG_CHECK_LAUNCH("fg_attention_combine");
+  return 0;
+}
+#else
+extern "C" int fg_attention_decode_tma_supported() { return 0; }
+#endif

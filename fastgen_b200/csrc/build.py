@@ -42,6 +42,7 @@ CORE_SOURCES = [
     "gemm_f32.cu",
     "gemm_skinny.cu",
     "sampling.cu",
+    "tensor_map.cu",
 ]
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -48,6 +48,7 @@ _CORE_SIGNATURES = {
     "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
     "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
+    "fg_make_kv_tensor_map": [_P, _P, _I, _I, _I, _I, _I, _I],
 }
 
 _ATTN_SIGNATURES = {
@@ -55,6 +56,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P],
+    "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
+                                     _F, _P, ctypes.c_longlong, _I, _P, _P],
 }
 
 SKINNY_MAX_M = 32     # most tokens the weight-streaming product takes
@@ -75,6 +78,15 @@ def _declare(lib: ctypes.CDLL, signatures) -> None:
 
 class KernelError(RuntimeError):
     pass
+
+
+class TensorMap:
+    """A 128-byte TMA descriptor kept on the host (64-byte aligned)."""
+
+    def __init__(self) -> None:
+        self._raw = ctypes.create_string_buffer(128 + 64)
+        addr = ctypes.addressof(self._raw)
+        self.ptr = (addr + 63) & ~63
 
 
 def _check(lib: ctypes.CDLL, rc: int) -> None:
@@ -273,14 +285,33 @@ class Ops:
             buf = self._scratch[size] = torch.empty(size, dtype=torch.float32, device=self.device)
         return buf
 
-    def attention(self, q, out, k_pages, v_pages, block_table, page_size: int, ctx,
-                  n_heads: int, n_kv_heads: int, head_dim: int,
+    def make_kv_tensor_maps(self, k_pool, v_pool, page_size: int):
+        """Tensor maps of a key and a value pool [layers, pages, kv heads, page,
+        head size], or ``None`` where the tiled-load kernels do not apply."""
+        n_layers, n_pages, n_kv_heads, page, head_dim = k_pool.shape
+        if (k_pool.dtype != torch.bfloat16 or head_dim % 64 != 0 or page_size < 8
+                or page_size & (page_size - 1)):
+            return None
+        maps = []
+        for pool in (k_pool, v_pool):
+            tm = TensorMap()
+            _check(self.lib, self.lib.fg_make_kv_tensor_map(
+                tm.ptr, _ptr(pool), n_layers, n_pages, n_kv_heads, page_size, head_dim,
+                min(page_size, DECODE_SPLIT)))
+            Ops.launches -= 1  # not a kernel
+            maps.append(tm)
+        return tuple(maps)
+
+    def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
                   window: Optional[int], scale: float) -> None:
-        """Paged causal attention of the step's query tokens (``ctx`` is the
-        step's context).  bfloat16 runs on the tensor cores: prompt portions in
-        one kernel, single tokens in a split-and-combine pair; float32 runs one
-        CUDA-core kernel for all."""
+        """Paged causal attention of the step's query tokens; ``memory`` is the
+        run's :class:`~fastgen_b200.cache.LayerMemory`, ``ctx`` the step's
+        context.  bfloat16 runs on the tensor cores: prompt portions in one
+        kernel, single tokens in a split-and-combine pair (with tiled TMA loads
+        where the shapes allow); float32 runs one CUDA-core kernel for all."""
         lib = attn(head_dim)
+        k_pages, v_pages, block_table, page_size = (
+            memory.k_pages, memory.v_pages, memory.block_table, memory.page_size)
         assert q.stride(1) == 1 and out.stride(1) == 1
         common = (_ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size,
                   k_pages.shape[0], _ptr(ctx.pos))
@@ -304,11 +335,17 @@ class Ops:
             max_splits = max(1, -(-singles.max_len // DECODE_SPLIT))
             floats = lib.fg_attention_decode_scratch_floats(singles.n, max_splits, n_heads)
             scratch = self._decode_scratch(floats)
-            _check(lib, lib.fg_attention_decode_bf16(
-                _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
-                _ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
-                int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits,
-                _ptr(self.status), _stream()))
+            tail = (_ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
+                    int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits,
+                    _ptr(self.status), _stream())
+            if memory.tensor_maps is not None and n_heads // n_kv_heads <= 16:
+                _check(lib, lib.fg_attention_decode_tma_bf16(
+                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
+                    memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table),
+                    block_table.shape[1], page_size, k_pages.shape[0], _ptr(ctx.pos), *tail))
+            else:
+                _check(lib, lib.fg_attention_decode_bf16(
+                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *tail))
             Ops.launches += 1  # the combine kernel
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,

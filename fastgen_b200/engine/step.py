@@ -159,6 +159,7 @@ class Engine:
             max_length=max_length,
             dtype=model.ops.act_dtype,
             device=self.device,
+            tensor_map_factory=model.ops.make_kv_tensor_maps,
         )
         self.memories = [self.cache.memory(e) for e in range(len(args.schedule))]
         self.last_h2d_bytes = 0

@@ -82,8 +82,7 @@ class GQAAttention(Mixer):
         )
         o = torch.empty((t, self.q_width), dtype=x.dtype, device=x.device)
         ops.attention(
-            q, o, memory.k_pages, memory.v_pages, memory.block_table, memory.page_size,
-            ctx, p.n_heads, p.n_kv_heads, p.head_dim, p.window, self.scale,
+            q, o, memory, ctx, p.n_heads, p.n_kv_heads, p.head_dim, p.window, self.scale,
         )
         return ops.linear(o, self.wo)
 

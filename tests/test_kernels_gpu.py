@@ -181,7 +181,7 @@ def test_rope_kv_write(ops32, dtype, hq, hkv, hd, page):
 # ---------------------------------------------------------------------------------
 # attention: a step context by hand, a paged cache with shuffled pages
 # ---------------------------------------------------------------------------------
-def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None):
+def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None, use_tma=True):
     """seqs: list of (cached, new) per request.  Returns (out, ref) for the new tokens."""
     from fastgen_b200.engine.step import StepContext
 
@@ -229,7 +229,11 @@ def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None):
     wide = torch.zeros(q.shape[0], q.shape[1] + 2 * hkv * hd, dtype=dtype, device=DEV)
     wide[:, : q.shape[1]] = q
     out = torch.full((q.shape[0], hq * hd), float("nan"), dtype=dtype, device=DEV)
-    ops.attention(wide[:, : q.shape[1]], out, kp, vp, table.to(DEV), page, ctx, hq, hkv, hd, window, hd ** -0.5)
+    from fastgen_b200.cache import LayerMemory
+    mem = LayerMemory(k_pages=kp, v_pages=vp, block_table=table.to(DEV), page_size=page)
+    if use_tma:
+        mem.tensor_maps = ops.make_kv_tensor_maps(kp[None], vp[None], page)
+    ops.attention(wide[:, : q.shape[1]], out, mem, ctx, hq, hkv, hd, window, hd ** -0.5)
     ops.check_status()
     return out.double().cpu(), torch.cat(refs)
 
@@ -243,6 +247,9 @@ CASES = [
     ([(517, 1), (130, 70)], 32, 8, 128, 64, None),
     ([(127, 1), (128, 1), (129, 1), (0, 1)], 5, 5, 16, 4, 100),
     ([(200, 1), (10, 50)], 40, 2, 32, 16, None),   # a group of 20 heads
+    ([(300, 1), (0, 1), (127, 1), (128, 1), (700, 1)], 8, 2, 64, 8, None),
+    ([(1000, 1), (255, 1), (256, 1), (90, 1)], 6, 2, 128, 16, 300),
+    ([(513, 1), (64, 1)], 16, 1, 128, 256, None),    # pages longer than a split
 ]
 
 
@@ -251,8 +258,9 @@ def test_attention(ops32, ops16, case):
     seqs, hq, hkv, hd, page, window = CASES[case]
     out, ref = _attention_case(ops32, seqs, hq, hkv, hd, page, window, case)
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5), float((out - ref).abs().max())
-    out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, case)
-    assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), float((out - ref).abs().max())
+    for use_tma in (True, False):  # tiled TMA loads where the shape allows, else (and also) cp.async
+        out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, case, use_tma=use_tma)
+        assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), float((out - ref).abs().max())
 
 
 @pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
@@ -282,12 +290,17 @@ def test_attention_missing_page_is_reported(ops16):
     ctx.pos = torch.tensor([20], dtype=torch.int32, device=DEV)
     ctx.req = torch.tensor([0], dtype=torch.int32, device=DEV)
     table = torch.tensor([[0, -1, 2]], dtype=torch.int32, device=DEV)  # page of positions 8..15 is missing
-    kp = torch.zeros(3, 1, 8, 16, dtype=torch.bfloat16, device=DEV)
-    q = torch.zeros(1, 16, dtype=torch.bfloat16, device=DEV)
-    out = torch.empty_like(q)
-    ops16.attention(q, out, kp, kp, table, 8, ctx, 1, 1, 16, None, 0.25)
-    with pytest.raises(KernelError, match="block-table"):
-        ops16.check_status()
+    from fastgen_b200.cache import LayerMemory
+    for hd in (16, 64):  # the cp.async kernel and the TMA kernel
+        kp = torch.zeros(3, 1, 8, hd, dtype=torch.bfloat16, device=DEV)
+        q = torch.zeros(1, hd, dtype=torch.bfloat16, device=DEV)
+        out = torch.empty_like(q)
+        mem = LayerMemory(k_pages=kp, v_pages=kp, block_table=table, page_size=8,
+                          tensor_maps=ops16.make_kv_tensor_maps(kp[None], kp[None], 8))
+        assert (mem.tensor_maps is not None) == (hd == 64)
+        ops16.attention(q, out, mem, ctx, 1, 1, hd, None, 0.25)
+        with pytest.raises(KernelError, match="block-table"):
+            ops16.check_status()
 
 
 # ---------------------------------------------------------------------------------
