@@ -207,3 +207,50 @@ extern "C" int fg_sample_uniform(unsigned long long seed, const long long* req_k
   FG_CHECK_LAUNCH("fg_sample_uniform");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// The sampler for callers that cannot allocate (see no_alloc.h).
+// ---------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// The scratch of fg_sample_noalloc: one array per GPU that loads this library, for
+// the life of the process.  In host code this name only stands for the symbol; its
+// device address is looked up once per device below.
+static __device__ __align__(256) float g_noalloc_scratch[FG_SAMPLE_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" long long fg_sample_noalloc_capacity(void) { return FG_SAMPLE_NOALLOC_MAX_FLOATS; }
+
+extern "C" int fg_sample_noalloc(const float* logits, int ld, int rows, int vocab, const float* temps,
+                                 float top_p, unsigned long long seed, const long long* req_keys,
+                                 const int* positions, int* out_tokens, float* out_logprobs,
+                                 cudaStream_t stream) {
+  if (rows == 0) return 0;
+  FG_CHECK_ARG(rows > 0 && vocab > 0 && ld >= vocab, "fg_sample_noalloc: bad sizes rows=%d vocab=%d ld=%d", rows,
+               vocab, ld);
+  FG_CHECK_ARG(top_p > 0.f, "fg_sample_noalloc: top_p must be positive, got %f", (double)top_p);
+  FG_CHECK_ARG((long long)rows * vocab <= (long long)FG_SAMPLE_NOALLOC_MAX_FLOATS,
+               "fg_sample_noalloc: rows * vocab = %lld exceeds the built-in scratch of %d floats; "
+               "use fg_sample with a buffer of your own",
+               (long long)rows * vocab, FG_SAMPLE_NOALLOC_MAX_FLOATS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  FG_CHECK_ARG(e == cudaSuccess && device >= 0 && device < kMaxDevices, "fg_sample_noalloc: no current device: %s",
+               cudaGetErrorString(e));
+  if (g_noalloc_ptr[device] == nullptr) {
+    // first call on this device: find where the array lives there (that device is current)
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    FG_CHECK_ARG(e == cudaSuccess && ptr != nullptr, "fg_sample_noalloc: cudaGetSymbolAddress failed: %s",
+                 cudaGetErrorString(e));
+    g_noalloc_ptr[device] = ptr;
+  }
+  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, temps, top_p, seed, req_keys, positions,
+                                              out_tokens, out_logprobs, g_noalloc_ptr[device]);
+  FG_CHECK_LAUNCH("fg_sample_noalloc");
+  return 0;
+}
