@@ -165,6 +165,7 @@ class Engine:
         self.last_h2d_bytes = 0
         if use_graphs is None:
             use_graphs = not bool(os.environ.get("FG_NO_CUDA_GRAPHS"))
+        use_graphs = use_graphs and all(b.mixer.graph_safe for b in model.blocks)
         # steps of single tokens replay a captured graph (as generate.py:296-347)
         self.graphs = _decode_graphs()(self, max_requests, num_cuda_graphs) if use_graphs else None
 

@@ -32,6 +32,7 @@ class GQAAttention(Mixer):
     """
 
     params: AttentionParams
+    graph_safe = True
 
     def __init__(self, spec) -> None:
         super().__init__(spec)

@@ -98,6 +98,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    #: whether ``forward`` only launches work that a CUDA graph may capture and
+    #: copes with padding lanes (slot -1).  Steps of a model with a mixer that
+    #: does not say so are never captured.
+    graph_safe = False
+
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 

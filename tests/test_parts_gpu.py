@@ -1,0 +1,311 @@
+"""Each part alone against the plain implementation; a toy architecture with a
+stateful mixer, registered from here without touching the package; long decoding;
+first tokens; the 8B layer shape."""
+
+import json
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as pl
+from fastgen_b200.config import LayerSpec, ModelArgs, PartSpec, ScheduleEntry, register_architecture
+from fastgen_b200.parts import (
+    AttentionParams, CacheSpec, Llama3Scaling, Mixer, NoPositionParams, RMSNormParams, RopeParams, StateSpec,
+    SwiGLUParams, WeightSpec, make_feed_forward, make_mixer, make_norm, make_position, register_mixer,
+)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops(dtype):
+    from fastgen_b200.csrc.ops import Ops
+    return Ops(dtype, DEV)
+
+
+def _tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(0)
+    norm = make_norm(PartSpec("rmsnorm", RMSNormParams(200, 3e-6), {"weight": "w"}))
+    assert [(s.name, s.shape) for s in norm.weight_specs()] == [("w", (200,))]
+    w = (1 + 0.1 * torch.randn(200, generator=g)).to(DEV, torch.bfloat16)
+    norm.bind({"weight": w}, ops)
+    h = torch.randn(5, 200, generator=g).to(DEV)
+    d = torch.randn(5, 200, generator=g).to(DEV, dtype)
+    ref = pl.rmsnorm(h.double() + d.double(), w.double(), 3e-6)
+    out = norm.add_forward(h, d)
+    assert out.dtype == dtype and torch.allclose(out.double(), ref, **_tol(dtype))
+    assert torch.allclose(norm.forward(h).double(), ref, **_tol(dtype))  # h now holds the sum
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(1)
+    ffn = make_feed_forward(PartSpec("swiglu", SwiGLUParams(72, 200), {"w1": "a", "w3": "b", "w2": "c"}))
+    assert {(s.name, s.shape) for s in ffn.weight_specs()} == {("a", (200, 72)), ("b", (200, 72)), ("c", (72, 200))}
+    t = {k: (torch.randn(*s, generator=g) * 0.2).to(DEV, torch.bfloat16)
+         for k, s in (("w1", (200, 72)), ("w3", (200, 72)), ("w2", (72, 200)))}
+    ffn.bind(t, ops)
+    x = torch.randn(9, 72, generator=g).to(DEV, dtype)
+    ref = pl.swiglu(x.double(), t["w1"].double(), t["w3"].double(), t["w2"].double())
+    assert torch.allclose(ffn.forward(x, None).double(), ref, **_tol(dtype))
+
+
+def test_position_parts():
+    rope = make_position(PartSpec("rope", RopeParams(64, 500000.0, Llama3Scaling(8.0, 1.0, 4.0, 64))))
+    ref = pl.rope_freqs(64, 500000.0, dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                           original_max_position_embeddings=64))
+    assert torch.equal(rope.table(DEV).cpu(), ref)
+    assert make_position(PartSpec("none", NoPositionParams())).table(DEV) is None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("position", ["rope", "none"])
+def test_attention_part(dtype, position):
+    """The mixer alone: a prompt portion, then single tokens, through a cache of its own."""
+    from fastgen_b200.cache import CacheManager
+    from fastgen_b200.engine.step import StepContext
+
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(2)
+    dim, hq, hkv, hd, window = 72, 6, 2, 16, 20
+    pos_spec = (PartSpec("rope", RopeParams(hd, 10000.0)) if position == "rope"
+                else PartSpec("none", NoPositionParams()))
+    spec = PartSpec("gqa_attention", AttentionParams(dim, hq, hkv, hd, pos_spec, window),
+                    {"wq": "q", "wk": "k", "wv": "v", "wo": "o"})
+    mixer = make_mixer(spec)
+    assert mixer.cache_spec() == CacheSpec(hkv, hd, window) and mixer.state_spec() is None
+    w = {k: (torch.randn(*s, generator=g) * 0.3).to(torch.bfloat16)
+         for k, s in (("wq", (hq * hd, dim)), ("wk", (hkv * hd, dim)), ("wv", (hkv * hd, dim)), ("wo", (dim, hq * hd)))}
+    mixer.bind({k: v.to(DEV) for k, v in w.items()}, ops)
+    cache = CacheManager([mixer.cache_spec()], [None], [None], 8, 12, 2, 96, dtype=dtype, device=DEV,
+                         tensor_map_factory=ops.make_kv_tensor_maps)
+    x = torch.randn(50, dim, generator=g).to(dtype)
+    # plain: project, rotate, attend over the whole sequence
+    xd = x.double()
+    q = (xd @ pl.permute_qk_rows(w["wq"].double(), hq).T).view(50, hq, hd)
+    k = (xd @ pl.permute_qk_rows(w["wk"].double(), hkv).T).view(50, hkv, hd)
+    v = (xd @ w["wv"].double().T).view(50, hkv, hd)
+    if position == "rope":
+        freqs = pl.rope_freqs(hd, 10000.0, None)
+        q, k = pl.apply_rope(q, torch.arange(50), freqs), pl.apply_rope(k, torch.arange(50), freqs)
+    ref = pl.causal_attention(q, k, v, hd ** -0.5, window).reshape(50, hq * hd) @ w["wo"].double().T
+    req = cache.admit("r")
+    outs, start = [], 0
+    for n in (30, 1, 1, 7, 1, 10):
+        cache.reserve(req, start + n)
+        cache.flush_tables()
+        ctx = StepContext(DEV)
+        ctx.host_seq_slot, ctx.host_seq_cached, ctx.host_seq_start = [req.slot], [start], [0, n]
+        ctx.pos = torch.arange(start, start + n, dtype=torch.int32, device=DEV)
+        ctx.req = torch.full((n,), req.slot, dtype=torch.int32, device=DEV)
+        ctx.n_tokens = n
+        outs.append(mixer.forward(x[start:start + n].to(DEV), ctx, cache.memory(0)))
+        cache.advance(req, start + n)
+        start += n
+    ops.check_status()
+    out = torch.cat(outs).double().cpu()
+    assert torch.allclose(out, ref, **_tol(dtype)), float((out - ref).abs().max())
+    assert len(req.pages[0]) <= 4  # the window gave pages back
+
+
+# ---------------------------------------------------------------------------------
+# a toy architecture: a mixer with state of its own, a layer that runs twice, and a
+# run that reads another run's cache
+# ---------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RunningMeanParams:
+    dim: int
+
+
+class RunningMeanMixer(Mixer):
+    """y_t = W * mean(x_0 .. x_t).  State per request: the running sum and the count."""
+
+    def weight_specs(self):
+        d = self.params.dim
+        return [WeightSpec(self.names["w"], (d, d), ("normal", 0.2))]
+
+    def state_spec(self):
+        return StateSpec((self.params.dim + 1,))
+
+    def bind(self, tensors, ops):
+        self.ops = ops
+        self.w = tensors["w"].float()
+
+    def forward(self, x, ctx, memory):
+        d = self.params.dim
+        out = torch.empty(x.shape[0], d, dtype=torch.float32, device=x.device)
+        for b, slot in enumerate(ctx.host_seq_slot):
+            s, e = ctx.host_seq_start[b], ctx.host_seq_start[b + 1]
+            state = memory.state[slot]
+            sums = torch.cumsum(x[s:e].float(), 0) + state[:d]
+            counts = state[d] + torch.arange(1, e - s + 1, device=x.device, dtype=torch.float32)
+            out[s:e] = (sums / counts[:, None]) @ self.w.T
+            state[:d] = sums[-1]
+            state[d] = counts[-1]
+        return out.to(x.dtype)
+
+
+def _toy_args(cfg):
+    d, v = cfg["hidden_size"], cfg["vocab_size"]
+    att = AttentionParams(d, 4, 2, 16, PartSpec("rope", RopeParams(16, 10000.0)))
+
+    def norm(name):
+        return PartSpec("rmsnorm", RMSNormParams(d, 1e-5), {"weight": name})
+
+    def ffn(i):
+        return PartSpec("swiglu", SwiGLUParams(d, 96), {"w1": f"l{i}.w1", "w3": f"l{i}.w3", "w2": f"l{i}.w2"})
+
+    def attn(i):
+        return PartSpec("gqa_attention", att, {"wq": f"l{i}.q", "wk": f"l{i}.k", "wv": f"l{i}.v", "wo": f"l{i}.o"})
+
+    layers = [
+        LayerSpec("prenorm", PartSpec("running_mean", RunningMeanParams(d), {"w": "l0.mix"}), norm("l0.n1"), ffn(0), norm("l0.n2")),
+        LayerSpec("prenorm", attn(1), norm("l1.n1"), ffn(1), norm("l1.n2")),
+        LayerSpec("prenorm", attn(2), norm("l2.n1"), ffn(2), norm("l2.n2")),
+    ]
+    # layer 0 runs twice (two states), layer 2 reads the cache layer 1's run wrote
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, kv_from=1)]
+    return ModelArgs("ToyForCausalLM", d, v, cfg["max_position_embeddings"], False, "emb", "out",
+                     tuple(layers), tuple(schedule), norm("final"))
+
+
+def _toy_plain(w, tokens):
+    """The toy model, whole sequence, float64."""
+    def block_ffn(h, i):
+        f = pl.rmsnorm(h, w[f"l{i}.n2"], 1e-5)
+        return h + pl.swiglu(f, w[f"l{i}.w1"], w[f"l{i}.w3"], w[f"l{i}.w2"])
+
+    def mean_layer(h):
+        a = pl.rmsnorm(h, w["l0.n1"], 1e-5)
+        cm = torch.cumsum(a, 0) / torch.arange(1, a.shape[0] + 1, dtype=a.dtype)[:, None]
+        return block_ffn(h + cm @ w["l0.mix"].T, 0)
+
+    t = len(tokens)
+    freqs = pl.rope_freqs(16, 10000.0, None)
+    pos = torch.arange(t)
+    h = w["emb"][torch.tensor(tokens)]
+    h = mean_layer(h)
+    a = pl.rmsnorm(h, w["l1.n1"], 1e-5)
+    k = pl.apply_rope((a @ pl.permute_qk_rows(w["l1.k"], 2).T).view(t, 2, 16), pos, freqs)
+    v = (a @ w["l1.v"].T).view(t, 2, 16)
+    q = pl.apply_rope((a @ pl.permute_qk_rows(w["l1.q"], 4).T).view(t, 4, 16), pos, freqs)
+    h = block_ffn(h + pl.causal_attention(q, k, v, 0.25).reshape(t, 64) @ w["l1.o"].T, 1)
+    h = mean_layer(h)
+    a = pl.rmsnorm(h, w["l2.n1"], 1e-5)
+    q = pl.apply_rope((a @ pl.permute_qk_rows(w["l2.q"], 4).T).view(t, 4, 16), pos, freqs)
+    h = block_ffn(h + pl.causal_attention(q, k, v, 0.25).reshape(t, 64) @ w["l2.o"].T, 2)  # layer 1's keys and values
+    return pl.rmsnorm(h, w["final"], 1e-5) @ w["out"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
+    from safetensors.torch import load_file
+    from fastgen_b200.weights import write_random_model
+
+    register_mixer("running_mean", RunningMeanMixer)
+    register_architecture("ToyForCausalLM", _toy_args)
+    cfg = dict(architectures=["ToyForCausalLM"], hidden_size=64, vocab_size=97, max_position_embeddings=256)
+    model_dir = write_random_model(tmp_path / "toy", cfg, seed=11, norm_jitter=0.1, std=0.1)
+    w = {k: v.double() for k, v in load_file(str(model_dir / "model.safetensors")).items()}
+    reqs = {f"t{i}": H.random_tokens(97, n, 40 + i) for i, n in enumerate([9, 33, 50, 21, 40, 12])}
+    steps = H.plan_mixed(reqs, seed=3, max_live=3)
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page_size=8,
+                                   max_tokens=H.max_live_tokens(steps, 8), max_requests=3)
+    assert engine.graphs is None  # a mixer that does not declare itself graph-safe is never captured
+    assert len(engine.cache.groups) == 1 and engine.cache.groups[0].entries == [1]
+    assert [s is not None for s in engine.cache.states] == [True, False, True, False]
+    got = H.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        ref = _toy_plain(w, toks).numpy()
+        for p, row in got[rid].items():
+            err = np.abs(row - ref[p]).max()
+            tol = 1e-4 if dtype == torch.float32 else 0.02 * max(1.0, np.abs(ref[p]).max())
+            assert err <= tol, (rid, p, err)
+
+
+# ---------------------------------------------------------------------------------
+# long decoding and first tokens
+# ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
+def test_long_decoding(tmp_path, name, dtype):
+    """A short prompt, then hundreds of single tokens: every page edge and every edge of
+    the key splits is crossed one token at a time (captured graphs included)."""
+    model_dir = H.make_model_dir(tmp_path, name)
+    vocab = H.CONFIGS[name][0]["vocab_size"]
+    reqs = {"long": H.random_tokens(vocab, 330, 9), "other": H.random_tokens(vocab, 150, 10)}
+    steps, n = [], 0
+    steps.append(dict(step=n, entries=[dict(id="long", tokens=reqs["long"][:3], want=[0, 1, 2])], end=[])); n += 1
+    for p in range(3, 330):
+        entries = [dict(id="long", tokens=[reqs["long"][p]], want=[0])]
+        q = p - 100  # a second request joins later and decodes beside the first
+        if 0 <= q < 150:
+            entries.append(dict(id="other", tokens=[reqs["other"][q]], want=[0]))
+        steps.append(dict(step=n, entries=entries, end=[])); n += 1
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page_size=16, max_tokens=512)
+    H.compare(model_dir, reqs, H.collect(steps, outputs), dtype)
+    assert engine.graphs is not None and engine.graphs.replays >= 300
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_first_tokens(tmp_path, dtype):
+    """Position 0 alone, then positions 1, 2, 3 one by one, for requests that start in different steps."""
+    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    reqs = {f"f{i}": H.random_tokens(256, 4, 60 + i) for i in range(3)}
+    steps = []
+    for s in range(6):
+        entries = [dict(id=rid, tokens=[toks[s - i]], want=[0]) for i, (rid, toks) in enumerate(reqs.items())
+                   if 0 <= s - i < 4]
+        steps.append(dict(step=s, entries=entries, end=[]))
+    outputs, _ = H.run_engine(model_dir, dtype, steps, page_size=8, max_tokens=64)
+    H.compare(model_dir, reqs, H.collect(steps, outputs), dtype)
+
+
+# ---------------------------------------------------------------------------------
+# the sizes of a Llama-3.1-8B layer (two layers, a small vocabulary)
+# ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_8b_layer_shape(tmp_path, dtype):
+    cfg = dict(
+        architectures=["LlamaForCausalLM"], hidden_size=4096, intermediate_size=14336, num_hidden_layers=2,
+        num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, vocab_size=1031,
+        tie_word_embeddings=False, rope_theta=500000.0,
+        rope_scaling=dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192),
+        max_position_embeddings=131072,
+    )
+    from fastgen_b200.weights import write_random_model
+    model_dir = write_random_model(tmp_path / "big", cfg, seed=4)
+    toks = H.random_tokens(1031, 150, 5)
+    other = H.random_tokens(1031, 70, 6)
+    ref = pl.forward(pl.read_model(model_dir, torch.float64), toks).numpy()
+    ref_other = pl.forward(pl.read_model(model_dir, torch.float64), other).numpy()
+    steps = [
+        dict(step=0, entries=[dict(id="a", tokens=toks[:100], want=list(range(100)))], end=[]),
+        dict(step=1, entries=[dict(id="a", tokens=toks[100:130], want=list(range(30))),
+                              dict(id="b", tokens=other[:69], want=list(range(69)))], end=[]),
+    ]
+    for p in range(130, 150):
+        e = [dict(id="a", tokens=[toks[p]], want=[0])]
+        if p == 130:
+            e.append(dict(id="b", tokens=[other[69]], want=[0]))
+        steps.append(dict(step=len(steps), entries=e, end=["b"] if p == 130 else []))
+    outputs, _ = H.run_engine(model_dir, dtype, steps, page_size=64, max_tokens=512)
+    got = H.collect(steps, outputs)
+    for rows, r in ((got["a"], ref), (got["b"], ref_other)):
+        for p, row in rows.items():
+            err = np.abs(row - r[p]).max()
+            tol = 1e-4 if dtype == torch.float32 else 0.02 * max(1.0, np.abs(r[p]).max())
+            assert err <= tol, (p, err)
+            if dtype == torch.float32 and np.sort(r[p])[-1] - np.sort(r[p])[-2] > 2e-4:
+                assert row.argmax() == r[p].argmax()
