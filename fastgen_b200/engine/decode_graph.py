@@ -11,6 +11,7 @@ every kernel treats as "no request" (nothing is written to any page).
 from __future__ import annotations
 
 import bisect
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -69,7 +70,11 @@ class _Bucket:
 
 class DecodeGraphs:
     def __init__(self, engine, max_batch: int, num_graphs: int) -> None:
-        self.engine = engine
+        # no reference back to the engine: graphs must not sit in a reference cycle,
+        # or the garbage collector may destroy them while another capture is running
+        self.model = engine.model
+        self.memories = engine.memories
+        self.device = engine.device
         self.sizes = bucket_sizes(max_batch, num_graphs)
         self.buckets: Dict[tuple, _Bucket] = {}
         self.pool = None
@@ -87,7 +92,7 @@ class DecodeGraphs:
         splits = 1 << (splits - 1).bit_length()
         b = self.buckets.get((size, splits))
         if b is None:
-            b = self.buckets[(size, splits)] = _Bucket(size, splits * DECODE_SPLIT, self.engine.device)
+            b = self.buckets[(size, splits)] = _Bucket(size, splits * DECODE_SPLIT, self.device)
         slot = b.ring_next
         b.ring_next = (slot + 1) % _RING
         if b.ring_events[slot] is not None:
@@ -109,16 +114,24 @@ class DecodeGraphs:
         ev = torch.cuda.Event()
         ev.record()
         b.ring_events[slot] = ev
-        model, memories = self.engine.model, self.engine.memories
+        model, memories = self.model, self.memories
         if b.graph is None:
-            ctx = b.context(self.engine.device)
+            ctx = b.context(self.device)
             # once eagerly (libraries load, attributes get set), then capture
             model.forward(ctx, memories)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = Ops.launches
-            with torch.cuda.graph(graph, pool=self.pool):
-                b.logits = model.forward(ctx, memories)
+            # the collector stays off while capturing: destroying an old graph or
+            # freeing device memory in the middle of a capture would invalidate it
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self.pool):
+                    b.logits = model.forward(ctx, memories)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             b.n_kernels = Ops.launches - before
             if self.pool is None:
                 self.pool = graph.pool()

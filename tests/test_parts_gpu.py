@@ -115,7 +115,11 @@ def test_attention_part(dtype, position):
         start += n
     ops.check_status()
     out = torch.cat(outs).double().cpu()
-    assert torch.allclose(out, ref, **_tol(dtype)), float((out - ref).abs().max())
+    # errors are judged against the outputs' scale (|y| is about 10 here): float32
+    # rounding of sums of that size is about 1e-6 of it
+    scale = float(ref.abs().max())
+    err = float((out - ref).abs().max())
+    assert err <= (1e-5 if dtype == torch.float32 else 2e-2) * scale, (err, scale)
     assert len(req.pages[0]) <= 4  # the window gave pages back
 
 
