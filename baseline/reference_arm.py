@@ -76,6 +76,7 @@ def run(args, cfg: dict) -> dict:
         torch.manual_seed(777)
         device = torch.device("cuda:0")
         torch.cuda.set_device(device)
+        torch.set_default_device(device)  # as the reference's own tools do (fastgen/tools/chat.py:47-48)
         k, w, batch, ctx = args.steps, args.warmup, args.batch, args.context
         prompt_len = max(1, ctx - k - w)
         block = 256  # the reference's default cache_block
@@ -83,10 +84,11 @@ def run(args, cfg: dict) -> dict:
         gen_args = GenArgs(use_sampling=False, max_batch=batch, max_seq=max(batch * per_lane, 2048 + 2 * block),
                            max_gen=k + w, host_cache_gb=0)
         fg = Fastgen.build(RandomLoader(), gen_args, tp_mesh=None, device=device, profile_sig=None)
-        g = torch.Generator().manual_seed(4)
+        g = torch.Generator(device="cpu").manual_seed(4)
 
         def prompts(n, length):
-            return [torch.randint(0, cfg["vocab_size"], (length,), generator=g).tolist() for _ in range(n)]
+            return [torch.randint(0, cfg["vocab_size"], (length,), generator=g, device="cpu").tolist()
+                    for _ in range(n)]
 
         def generate(ps, max_gen):
             q = queue.Queue()
