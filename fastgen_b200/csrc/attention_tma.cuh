@@ -35,7 +35,7 @@ __device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, i
 // byte offset of the 16-byte piece `chunk` (0..7) of `row` inside a swizzled half
 __device__ __forceinline__ int swz(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-template <int HD, int NT>
+template <int HD, int NT, int HALF = HALF_BYTES>
 __device__ __forceinline__ void qk_product_swz(float (&s)[NT][4], const uint32_t (&qf)[HD / 16][4],
                                                const unsigned char* ks, int row0, int lane) {
 #pragma unroll
@@ -44,7 +44,7 @@ __device__ __forceinline__ void qk_product_swz(float (&s)[NT][4], const uint32_t
     for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
 #pragma unroll
   for (int kk = 0; kk < HD / 16; ++kk) {
-    const unsigned char* half = ks + (kk / 4) * HALF_BYTES;
+    const unsigned char* half = ks + (kk / 4) * HALF;
     const int chunk = (kk % 4) * 2 + ((lane >> 3) & 1);
 #pragma unroll
     for (int np = 0; np < NT / 2; ++np) {
@@ -57,7 +57,7 @@ __device__ __forceinline__ void qk_product_swz(float (&s)[NT][4], const uint32_t
   }
 }
 
-template <int HD, int NT>
+template <int HD, int NT, int HALF = HALF_BYTES>
 __device__ __forceinline__ void pv_product_swz(float (&o)[HD / 8][4], const float (&p)[NT][4],
                                                const unsigned char* vs, int row0, int lane) {
 #pragma unroll
@@ -71,7 +71,7 @@ __device__ __forceinline__ void pv_product_swz(float (&o)[HD / 8][4], const floa
 #pragma unroll
     for (int np = 0; np < HD / 16; ++np) {
       uint32_t b[4];
-      const unsigned char* half = vs + (np / 4) * HALF_BYTES;
+      const unsigned char* half = vs + (np / 4) * HALF;
       const int chunk = (np % 4) * 2 + (lane >> 4);
       ldmatrix_x4_trans(b, half + swz(row, chunk));
       mma_16816(o[2 * np], a, b[0], b[1]);
@@ -241,6 +241,237 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     if (d == 0) {
       dst[HD] = mm;
       dst[HD + 1] = ll;
+    }
+  }
+}
+
+
+// ---------------------------------------------------------------------------------
+// prompt portions with tiled TMA loads
+// ---------------------------------------------------------------------------------
+constexpr int PF_ROWS = 128;   // query rows per block (8 warps x 16)
+constexpr int PF_KEYS = 64;    // key positions per tile
+constexpr int PF_THREADS = 256;
+constexpr int PF_HALF = PF_KEYS * 128;  // bytes of one 64-element half of a tile
+
+// Online softmax on raw scores: the scale is folded into the exponent,
+// p = 2^((s - m) * c) with c = scale * log2(e); m is kept in raw units.
+template <int HD, int NT>
+__device__ __forceinline__ void softmax_step_raw(float (&s)[NT][4], float (&o)[HD / 8][4], float (&m)[2],
+                                                 float (&l)[2], float c) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * h], s[nt][2 * h + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    float alpha = 1.f, sum = 0.f;
+    if (m_new == -INFINITY) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) s[nt][2 * h] = s[nt][2 * h + 1] = 0.f;
+    } else {
+      alpha = (m[h] == -INFINITY) ? 0.f : exp2f((m[h] - m_new) * c);
+      const float mc = m_new * c;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float p0 = exp2f(fmaf(s[nt][2 * h], c, -mc));
+        const float p1 = exp2f(fmaf(s[nt][2 * h + 1], c, -mc));
+        s[nt][2 * h] = p0;
+        s[nt][2 * h + 1] = p1;
+        sum += p0 + p1;
+      }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    l[h] = l[h] * alpha + sum;
+    m[h] = m_new;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      o[nt][2 * h] *= alpha;
+      o[nt][2 * h + 1] *= alpha;
+    }
+  }
+}
+
+template <int HD>
+constexpr size_t prefill_tma_smem_bytes() {
+  // two stages of keys and values (unpadded, swizzled), padded queries, alignment slack
+  return (size_t)2 * 2 * PF_KEYS * HD * 2 + sizeof(__nv_bfloat16) * Tile<HD>::LD * PF_ROWS + 1024;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PF_THREADS)
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                             int layer, const __nv_bfloat16* __restrict__ q, int q_stride,
+                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ block_table,
+                             int table_width, int page_size, int n_pages, const int* __restrict__ pos,
+                             const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
+                             const int* __restrict__ tile_ntok, int n_tiles_total, int group,
+                             int heads_per_block, int window, float scale_log2, int* status) {
+  static_assert(HD % 64 == 0, "tiled loads take 64-element halves");
+  constexpr int LD = Tile<HD>::LD;
+  constexpr int NT = PF_KEYS / 8;
+  constexpr int HALVES = HD / 64;
+  constexpr int STAGE_BYTES = HALVES * PF_HALF;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  unsigned char* Ks = smem;                     // [2 stages][HALVES][64 rows][128 B]
+  unsigned char* Vs = Ks + 2 * STAGE_BYTES;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(Vs + 2 * STAGE_BYTES);
+  __shared__ __align__(8) uint64_t full[2];
+  __shared__ int row_pos[PF_ROWS];
+
+  // the heaviest tiles (the latest tokens of long portions come last in the list) start first
+  const int tile = n_tiles_total - 1 - blockIdx.x;
+  const int g = blockIdx.y, sub = blockIdx.z;
+  const int b = tile_req[tile];
+  const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (b < 0) return;
+
+  auto row_token = [&](int r) { return r / heads_per_block; };
+  auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
+  auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
+
+  if (tid < PF_ROWS) row_pos[tid] = row_valid(tid) ? pos[tok0 + row_token(tid)] : -1;
+  constexpr int CH = HD / 8;
+  for (int i = tid; i < PF_ROWS * CH; i += PF_THREADS) {
+    const int r = i / CH, c = i - r * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row_valid(r))
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(tok0 + row_token(r)) * q_stride +
+                                          (g * group + row_head(r)) * HD + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
+  }
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // tokens of a tile are consecutive positions: the extremes are at its ends
+  const int min_pos = row_pos[0];
+  const int max_pos = min_pos + ntok - 1;
+  const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
+  const int k_lo = k_begin / PF_KEYS * PF_KEYS;
+  const int k_end = max_pos + 1;
+  const int n_tiles = (k_end - k_lo + PF_KEYS - 1) / PF_KEYS;
+  const int* table_row = block_table + (size_t)b * table_width;
+  const int box_rows = min(page_size, PF_KEYS);
+  const int n_boxes = PF_KEYS / box_rows;
+
+  // page of box i of key tile t, or -1 when the box holds no position in [k_begin, k_end)
+  auto box_page = [&](int t, int i) {
+    const int j0 = k_lo + t * PF_KEYS + i * box_rows;
+    if (j0 >= k_end || j0 + box_rows <= k_begin) return -1;
+    const int logical = j0 / page_size;
+    const int page = logical < table_width ? table_row[logical] : -1;
+    if (page < 0 || page >= n_pages) {
+      if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+      return -1;
+    }
+    return page;
+  };
+  auto issue = [&](int t) {  // thread 0 only
+    const int stage = t & 1;
+    int n_valid = 0;
+    for (int i = 0; i < n_boxes; ++i) n_valid += box_page(t, i) >= 0;
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    mbar_arrive_expect(&full[stage], 2 * n_valid * box_rows * HD * 2);
+    const int slot0 = (k_lo + t * PF_KEYS) % page_size;
+    for (int i = 0; i < n_boxes; ++i) {
+      const int page = box_page(t, i);
+      if (page < 0) continue;
+      const int slot = page_size > PF_KEYS ? slot0 : 0;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_5d(Ks + stage * STAGE_BYTES + h * PF_HALF + i * box_rows * 128, &k_map, h * 64, slot, g, page,
+                    layer, &full[stage]);
+        tma_load_5d(Vs + stage * STAGE_BYTES + h * PF_HALF + i * box_rows * 128, &v_map, h * 64, slot, g, page,
+                    layer, &full[stage]);
+      }
+    }
+  };
+  // boxes that are not loaded must hold zeros (only at the ends of a request with small pages)
+  auto zero_missing = [&](int t) -> bool {
+    bool any = false;
+    for (int i = 0; i < n_boxes; ++i) {
+      if (box_page(t, i) >= 0) continue;
+      any = true;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int h = 0; h < HALVES; ++h)
+        for (int c = tid; c < box_rows * 8; c += PF_THREADS) {
+          *reinterpret_cast<uint4*>(Ks + (t & 1) * STAGE_BYTES + h * PF_HALF + i * box_rows * 128 + c * 16) = z;
+          *reinterpret_cast<uint4*>(Vs + (t & 1) * STAGE_BYTES + h * PF_HALF + i * box_rows * 128 + c * 16) = z;
+        }
+    }
+    return any;
+  };
+  if (tid == 0) issue(0);
+
+  const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+  const int p0 = row_pos[r0], p1 = row_pos[r1];
+  int warp_max = -1, warp_min = 0x7fffffff;
+  bool warp_full = true;  // all 16 rows of the warp hold a query
+  for (int r = warp * 16; r < warp * 16 + 16; ++r) {
+    const int p = row_pos[r];
+    warp_max = max(warp_max, p);
+    if (p >= 0) warp_min = min(warp_min, p); else warp_full = false;
+  }
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk)
+    ldmatrix_x4(qf[kk], Qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + ((lane >> 4) << 3));
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  for (int t = 0; t < n_tiles; ++t) {
+    if (t + 1 < n_tiles && tid == 0) issue(t + 1);  // its stage was released by the barrier below
+    if (zero_missing(t)) __syncthreads();
+    mbar_wait(&full[t & 1], (t >> 1) & 1, status);
+    const int k0 = k_lo + t * PF_KEYS;
+    if (k0 <= warp_max) {
+      const unsigned char* ks = Ks + (t & 1) * STAGE_BYTES;
+      const unsigned char* vs = Vs + (t & 1) * STAGE_BYTES;
+      float s[NT][4];
+      qk_product_swz<HD, NT, PF_HALF>(s, qf, ks, 0, lane);
+      // only tiles that touch the diagonal, the window's edge or an unused row need the mask
+      const bool need_mask = !warp_full || k0 + PF_KEYS - 1 > warp_min ||
+                             (window > 0 && k0 <= warp_max - window);
+      if (need_mask) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = k0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+            const int p = (e < 2) ? p0 : p1;
+            const bool vis = p >= 0 && j <= p && (window <= 0 || j > p - window);
+            if (!vis) s[nt][e] = -INFINITY;
+          }
+      }
+      softmax_step_raw<HD, NT>(s, o, m, l, scale_log2);
+      pv_product_swz<HD, NT, PF_HALF>(o, s, vs, 0, lane);
+    }
+    __syncthreads();  // everyone is done with this stage before it is refilled
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = h ? r1 : r0;
+    if (!row_valid(r)) continue;
+    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(tok0 + row_token(r)) * out_stride + (g * group + row_head(r)) * HD;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      const int d = nt * 8 + 2 * (lane & 3);
+      *reinterpret_cast<__nv_bfloat162*>(dst + d) =
+          __floats2bfloat162_rn(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
     }
   }
 }

@@ -56,6 +56,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P],
+    "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
+                                      _I, _F, _P, _P],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, _P, _P],
 }
@@ -63,6 +65,7 @@ _ATTN_SIGNATURES = {
 SKINNY_MAX_M = 32     # most tokens the weight-streaming product takes
 SIMT_ROWS = 16       # query rows per block of the float32 attention kernel
 PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
+PREFILL_TMA_ROWS = 128  # ... of the bfloat16 prompt kernel with tiled TMA loads
 DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kernel
 
 
@@ -323,8 +326,17 @@ class Ops:
                 n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
                 _ptr(self.status), _stream()))
             return
-        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, PREFILL_ROWS), 2)
-        if tiles.n:
+        use_tma = memory.tensor_maps is not None
+        rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
+        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, rows), 2)
+        if tiles.n and use_tma:
+            _check(lib, lib.fg_attention_prefill_tma_bf16(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
+                memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
+                page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
+                _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+                _ptr(self.status), _stream()))
+        elif tiles.n:
             _check(lib, lib.fg_attention_prefill_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
                 _ptr(tiles.req), _ptr(tiles.tok0), _ptr(tiles.ntok), tiles.n,
@@ -338,7 +350,7 @@ class Ops:
             tail = (_ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
                     int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits,
                     _ptr(self.status), _stream())
-            if memory.tensor_maps is not None and n_heads // n_kv_heads <= 16:
+            if use_tma and n_heads // n_kv_heads <= 16:
                 _check(lib, lib.fg_attention_decode_tma_bf16(
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
                     memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table),

@@ -250,6 +250,9 @@ CASES = [
     ([(300, 1), (0, 1), (127, 1), (128, 1), (700, 1)], 8, 2, 64, 8, None),
     ([(1000, 1), (255, 1), (256, 1), (90, 1)], 6, 2, 128, 16, 300),
     ([(513, 1), (64, 1)], 16, 1, 128, 256, None),    # pages longer than a split
+    ([(0, 300), (190, 75), (63, 2), (7, 130)], 8, 2, 64, 8, None),     # prompt portions, small pages
+    ([(100, 200), (0, 129)], 6, 2, 128, 16, 90),                        # ... with a window
+    ([(250, 260)], 4, 1, 128, 256, None),
 ]
 
 
