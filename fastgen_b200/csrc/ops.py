@@ -66,6 +66,7 @@ SKINNY_MAX_M = 32     # most tokens the weight-streaming product takes
 SIMT_ROWS = 16       # query rows per block of the float32 attention kernel
 PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
 PREFILL_TMA_ROWS = 128  # ... of the bfloat16 prompt kernel with tiled TMA loads
+PREFILL_TMA_KEYS = 64   # key positions per tile of that kernel
 DECODE_SPLIT = 128   # key positions per split of the bfloat16 single-token kernel
 
 
@@ -295,14 +296,17 @@ class Ops:
         if (k_pool.dtype != torch.bfloat16 or head_dim % 64 != 0 or page_size < 8
                 or page_size & (page_size - 1)):
             return None
+        # the box (rows a TMA instruction brings) is part of the map: one pair of maps
+        # for the single-token kernel (128 positions a split), one for the prompt
+        # kernel (64 positions a tile)
         maps = []
-        for pool in (k_pool, v_pool):
-            tm = TensorMap()
-            _check(self.lib, self.lib.fg_make_kv_tensor_map(
-                tm.ptr, _ptr(pool), n_layers, n_pages, n_kv_heads, page_size, head_dim,
-                min(page_size, DECODE_SPLIT)))
-            Ops.launches -= 1  # not a kernel
-            maps.append(tm)
+        for box_rows in (min(page_size, DECODE_SPLIT), min(page_size, PREFILL_TMA_KEYS)):
+            for pool in (k_pool, v_pool):
+                tm = TensorMap()
+                _check(self.lib, self.lib.fg_make_kv_tensor_map(
+                    tm.ptr, _ptr(pool), n_layers, n_pages, n_kv_heads, page_size, head_dim, box_rows))
+                Ops.launches -= 1  # not a kernel
+                maps.append(tm)
         return tuple(maps)
 
     def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -331,8 +335,8 @@ class Ops:
         tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, rows), 2)
         if tiles.n and use_tma:
             _check(lib, lib.fg_attention_prefill_tma_bf16(
-                _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
-                memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[2].ptr,
+                memory.tensor_maps[3].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
                 page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
                 _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
                 _ptr(self.status), _stream()))

@@ -306,10 +306,17 @@ def test_8b_layer_shape(tmp_path, dtype):
         steps.append(dict(step=len(steps), entries=e, end=["b"] if p == 130 else []))
     outputs, _ = H.run_engine(model_dir, dtype, steps, page_size=64, max_tokens=512)
     got = H.collect(steps, outputs)
+    # bfloat16 bound for this width: every activation is rounded to 8 bits (2^-9 relative,
+    # about 0.1% rms) some twenty times on the way; the roundings add up like a random walk
+    # to about 1% of the logits' rms.  The test allows 3% in the l2 norm, and 5% of the
+    # largest logit for the worst of the 1,031 entries (about four sigma of the above).
     for rows, r in ((got["a"], ref), (got["b"], ref_other)):
         for p, row in rows.items():
             err = np.abs(row - r[p]).max()
-            tol = 1e-4 if dtype == torch.float32 else 0.02 * max(1.0, np.abs(r[p]).max())
-            assert err <= tol, (p, err)
-            if dtype == torch.float32 and np.sort(r[p])[-1] - np.sort(r[p])[-2] > 2e-4:
-                assert row.argmax() == r[p].argmax()
+            if dtype == torch.float32:
+                assert err <= 1e-4, (p, err)
+                if np.sort(r[p])[-1] - np.sort(r[p])[-2] > 2e-4:
+                    assert row.argmax() == r[p].argmax()
+            else:
+                assert np.linalg.norm(row - r[p]) <= 0.03 * np.linalg.norm(r[p]), (p, err)
+                assert err <= 0.05 * np.abs(r[p]).max(), (p, err)
