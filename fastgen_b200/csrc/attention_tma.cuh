@@ -322,6 +322,8 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(Vs + 2 * STAGE_BYTES);
   __shared__ __align__(8) uint64_t full[2];
   __shared__ int row_pos[PF_ROWS];
+  constexpr int PAGE_STAGE = 512;             // box page ids kept in shared memory at a time
+  __shared__ int box_pages[PAGE_STAGE];
 
   // the heaviest tiles (the latest tokens of long portions come last in the list) start first
   const int tile = n_tiles_total - 1 - blockIdx.x;
@@ -363,18 +365,29 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int box_rows = min(page_size, PF_KEYS);
   const int n_boxes = PF_KEYS / box_rows;
 
-  // page of box i of key tile t, or -1 when the box holds no position in [k_begin, k_end)
-  auto box_page = [&](int t, int i) {
-    const int j0 = k_lo + t * PF_KEYS + i * box_rows;
-    if (j0 >= k_end || j0 + box_rows <= k_begin) return -1;
-    const int logical = j0 / page_size;
-    const int page = logical < table_width ? table_row[logical] : -1;
-    if (page < 0 || page >= n_pages) {
-      if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
-      return -1;
+  // page of box x (counted over all key tiles), or -1 when the box holds no position in
+  // [k_begin, k_end); looked up for a stretch of tiles at a time so that the block-table
+  // reads are off the critical path of every tile
+  const int tiles_per_fill = PAGE_STAGE / n_boxes;
+  auto fill_pages = [&](int t_first) {
+    const int n = min(tiles_per_fill, n_tiles - t_first) * n_boxes;
+    for (int x = tid; x < n; x += PF_THREADS) {
+      const int j0 = k_lo + t_first * PF_KEYS + x * box_rows;
+      int page = -1;
+      if (j0 < k_end && j0 + box_rows > k_begin) {
+        const int logical = j0 / page_size;
+        page = logical < table_width ? table_row[logical] : -1;
+        if (page < 0 || page >= n_pages) {
+          if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+          page = -1;
+        }
+      }
+      box_pages[x] = page;
     }
-    return page;
   };
+  auto box_page = [&](int t, int i) { return box_pages[(t % tiles_per_fill) * n_boxes + i]; };
+  fill_pages(0);
+  __syncthreads();
   auto issue = [&](int t) {  // thread 0 only
     const int stage = t & 1;
     int n_valid = 0;
@@ -432,8 +445,18 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   for (int t = 0; t < n_tiles; ++t) {
+    // the copy of tile t+1 is issued one tile ahead; where t+1 starts a new stretch of
+    // page ids, the stretch is looked up first (tile t's ids are not needed any more:
+    // its copy is in flight and its missing boxes are zeroed before the look-up)
+    const bool missing = zero_missing(t);
+    if ((t + 1) % tiles_per_fill == 0 && t + 1 < n_tiles) {
+      __syncthreads();
+      fill_pages(t + 1);
+      __syncthreads();
+    } else if (missing) {
+      __syncthreads();
+    }
     if (t + 1 < n_tiles && tid == 0) issue(t + 1);  // its stage was released by the barrier below
-    if (zero_missing(t)) __syncthreads();
     mbar_wait(&full[t & 1], (t >> 1) & 1, status);
     const int k0 = k_lo + t * PF_KEYS;
     if (k0 <= warp_max) {

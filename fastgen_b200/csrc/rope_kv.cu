@@ -51,15 +51,16 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
                const int* __restrict__ req, const float* __restrict__ freqs, T* __restrict__ k_pages,
                T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim, int* status,
-               bool vec) {
+               bool vec, int items_per_thread) {
   const int t = blockIdx.x;
   const int r = req[t];
   if (r < 0) return;
   const int half = head_dim >> 1;
   const int n_q = n_heads * half, n_kv = (k != nullptr) ? n_kv_heads * half : 0;
-  const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
-  if (item >= n_q + 2 * n_kv) return;
   const int p = pos[t];
+  for (int it = 0; it < items_per_thread; ++it) {
+  const int item = (blockIdx.y * items_per_thread + it) * ROPE_THREADS + threadIdx.x;
+  if (item >= n_q + 2 * n_kv) return;
   if (item < n_q) {
     const int j = item % half;
     T* x = q + (size_t)t * q_stride + (item / half) * head_dim + 2 * j;
@@ -67,7 +68,7 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
     float s = 0.f, c = 1.f;
     if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
     store_pair<T>(x, make_float2(v.x * c - v.y * s, v.y * c + v.x * s), vec);
-    return;
+    continue;
   }
   const bool is_v = item >= n_q + n_kv;
   const int kv_item = item - n_q - (is_v ? n_kv : 0);
@@ -96,6 +97,7 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
     if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
     store_pair<T>(k_pages + dst, make_float2(kv.x * c - kv.y * s, kv.y * c + kv.x * s), vec);
   }
+  }
 }
 
 // q: [T, n_heads*head_dim] with row stride q_stride (elements), rotated in place.
@@ -113,7 +115,11 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
   FG_CHECK_ARG(k == nullptr || (k_pages && v_pages && block_table && page_size > 0),
                "fg_rope_kv_write: cache arguments missing");
   const int items = (n_heads + (k ? 2 * n_kv_heads : 0)) * head_dim / 2;
-  const dim3 grid(n_tokens, (items + ROPE_THREADS - 1) / ROPE_THREADS);
+  // few tokens: one pair a thread, many small blocks; many tokens: several pairs a
+  // thread, so that the number of blocks stays in the low thousands
+  int ipt = 1;
+  while (ipt < 16 && (long long)n_tokens * ((items + ROPE_THREADS * ipt - 1) / (ROPE_THREADS * ipt)) > 4096) ipt *= 2;
+  const dim3 grid(n_tokens, (items + ROPE_THREADS * ipt - 1) / (ROPE_THREADS * ipt));
   const int threads = ROPE_THREADS;
   FG_CHECK_ARG(grid.y <= 65535, "fg_rope_kv_write: too many heads");
   const size_t pair = dtype == FG_F32 ? 8 : 4;
@@ -123,12 +129,12 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
     rope_kv_kernel<float><<<grid, threads, 0, stream>>>(
         (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, pos, req, freqs,
         (float*)k_pages, (float*)v_pages, block_table, table_width, page_size, n_pages, n_heads,
-        n_kv_heads, head_dim, status, vec);
+        n_kv_heads, head_dim, status, vec, ipt);
   else if (dtype == FG_BF16)
     rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v,
         v_stride, pos, req, freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
-        table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec);
+        table_width, page_size, n_pages, n_heads, n_kv_heads, head_dim, status, vec, ipt);
   else
     FG_CHECK_ARG(false, "fg_rope_kv_write: bad dtype %d", dtype);
   FG_CHECK_LAUNCH("fg_rope_kv_write");
