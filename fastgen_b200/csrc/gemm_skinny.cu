@@ -4,13 +4,23 @@
 // With so few tokens the product is bound by reading W once from HBM.  The roles
 // of the operands are swapped for the tensor core: 16 rows of W are the "M" side
 // of mma.sync m16n8k16 and 8 tokens the "N" side, so no row of the instruction is
-// wasted on padding.  Fragments are loaded straight from global memory with
-// 16-byte loads (the k index inside an instruction is permuted identically for
-// both operands, which does not change the sum), so there is no shared-memory
-// staging and no barrier in the main loop; each thread keeps several loads in
-// flight.  A block owns 16 rows of W; its 8 warps split K in interleaved chunks
+// wasted on padding.  A thread's fragments are 16-byte pieces of W and x (the k
+// index inside an instruction is permuted identically for both operands, which
+// does not change the sum).  Every thread streams its own pieces through a ring
+// of cp.async stages in shared memory that only it reads back, so the main loop
+// has no barrier and many kilobytes per warp are in flight without holding
+// registers.  A block owns 16 rows of W; its 8 warps split K in interleaved chunks
 // of 64 and are summed in warp order at the end, so a row's result depends on
 // nothing but K.
+//
+// Two fused variants serve the decode step:
+//  * prologue "SiLU gate": x is [gate | up] of width 2K and the operand is
+//    silu(gate) * up computed on the fly (the feed-forward's down projection,
+//    fastgen/forward.py:495-496);
+//  * epilogue "QKV": the 16 output rows are 8 adjacent pairs of one head; they are
+//    rotated by the token's position (fastgen/kernels/rope.py:77-89), queries go
+//    to y, keys and values straight into their cache pages
+//    (fastgen/forward.py:449-460), replacing a separate kernel and a round trip.
 //
 // It stands where the reference calls F.linear on decode batches
 // (fastgen/forward.py:438-440,470,491-496,513); larger M goes to the library.
@@ -20,21 +30,44 @@ namespace {
 
 constexpr int ROWS = 16;   // rows of W per block
 constexpr int CHUNK = 64;  // k elements per warp step
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
+enum { PRO_PLAIN = 0, PRO_SILU = 1 };
+enum { EPI_PLAIN = 0, EPI_QKV = 1 };
+
+struct QkvEpilogue {
+  const int* pos;
+  const int* req;
+  const float* freqs;  // [head_dim / 2] or null
+  __nv_bfloat16* k_pages;
+  __nv_bfloat16* v_pages;
+  const int* block_table;
+  int table_width, page_size, n_pages;
+  int n_heads, n_kv_heads, head_dim;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// 16-byte asynchronous copy; `keep` asks for the line to stay in L1 (activations,
+// read by every warp) while weights, read once, bypass it.  !pred: zero-fill.
+template <bool KEEP>
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;
+  if (KEEP)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes)
+                 : "memory");
+  else
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes)
+                 : "memory");
 }
-__device__ __forceinline__ uint4 ldg_keep(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
+
 __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                     uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -44,74 +77,99 @@ __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, typename TO, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+// silu(g) * u on eight bfloat16 values, float32 arithmetic, one rounding
+__device__ __forceinline__ uint4 silu_gate8(uint4 g4, uint4 u4) {
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+  uint4 o4;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+    o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+  }
+  return o4;
+}
+
+// 16-byte pieces a thread copies per chunk (4 of W, the rest of x), ring depth, ring size
+template <int NT, int PRO>
+struct Ring {
+  static constexpr int PIECES = 4 + 2 * NT * (PRO == PRO_SILU ? 2 : 1);
+  static constexpr int STAGES = PIECES <= 8 ? 4 : (PIECES <= 12 ? 3 : 2);
+  static constexpr size_t BYTES = (size_t)STAGES * PIECES * THREADS * 16;
+};
+
+template <int NT, typename TO, int PRO, int EPI>
+__global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
-                   TO* __restrict__ y, int ldy, int M, int N, int K) {
+                   TO* __restrict__ y, int ldy, int M, int N, int K, QkvEpilogue qkv) {
+  constexpr int PIECES = Ring<NT, PRO>::PIECES;
+  constexpr int STAGES = Ring<NT, PRO>::STAGES;
+  constexpr int XP = PRO == PRO_SILU ? 2 : 1;  // x pieces per (token tile, half): gate and up, or one
+  extern __shared__ __align__(16) unsigned char ring_raw[];
+  uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [STAGES][PIECES][THREADS]
   __shared__ float red[WARPS][ROWS][NT * 8];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n0 = blockIdx.x * ROWS;
   const int r = lane >> 2, c = lane & 3;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  // rows beyond N and tokens beyond M read row 0 and are discarded at the end
+  // rows beyond N and tokens beyond M are zero-filled and discarded at the end
   const bool row_a = n0 + r < N, row_b = n0 + r + 8 < N;
   const __nv_bfloat16* wa = w + (size_t)(row_a ? n0 + r : 0) * ldw + c * 8;
   const __nv_bfloat16* wb = w + (size_t)(row_b ? n0 + r + 8 : 0) * ldw + c * 8;
   const __nv_bfloat16* xr[NT];
+  bool tok_ok[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = nt * 8 + r;
-    xr[nt] = x + (size_t)(tok < M ? tok : 0) * ldx + c * 8;
+    tok_ok[nt] = tok < M;
+    xr[nt] = x + (size_t)(tok_ok[nt] ? tok : 0) * ldx + c * 8;
   }
   float acc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
-  constexpr int UNROLL = NT <= 2 ? 4 : 2;
-  const int n_full = K / CHUNK;  // whole chunks: loads without predicates
-  int ch = warp;
-  // main loop: UNROLL chunks per warp step, every load issued before the first product
-  for (; ch + (UNROLL - 1) * WARPS < n_full; ch += WARPS * UNROLL) {
-    uint4 a_lo[UNROLL][2], a_hi[UNROLL][2], b[UNROLL][NT][2];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int k = (ch + u * WARPS) * CHUNK;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        a_lo[u][h] = ldg_stream(wa + k + h * 32);
-        a_hi[u][h] = ldg_stream(wb + k + h * 32);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) b[u][nt][h] = ldg_keep(xr[nt] + k + h * 32);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          mma(acc[nt], a_lo[u][h].x, a_hi[u][h].x, a_lo[u][h].y, a_hi[u][h].y, b[u][nt][h].x, b[u][nt][h].y);
-          mma(acc[nt], a_lo[u][h].z, a_hi[u][h].z, a_lo[u][h].w, a_hi[u][h].w, b[u][nt][h].z, b[u][nt][h].w);
-        }
-  }
-  // the remaining chunks, the last of which may be partial (K is a multiple of 8,
-  // so a 16-byte piece is all in or all out)
   const int n_chunks = (K + CHUNK - 1) / CHUNK;
-  for (; ch < n_chunks; ch += WARPS) {
-    const int k = ch * CHUNK;
+  const int my_chunks = warp < n_chunks ? (n_chunks - warp + WARPS - 1) / WARPS : 0;
+
+  // issue the copies of this thread's i-th chunk into stage i % STAGES
+  auto issue = [&](int i) {
+    uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
+    const int k = (warp + i * WARPS) * CHUNK;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int kk = k + h * 32;
-      const bool ok = kk + c * 8 < K;
-      const int ks = ok ? kk : 0;
-      uint4 al = ldg_stream(wa + ks), ah = ldg_stream(wb + ks);
-      if (!ok) al = ah = zero;
+      const bool ok = kk + c * 8 < K;  // K is a multiple of 8: a 16-byte piece is all in or all out
+      cp_async_16<false>(slot + (2 * h) * THREADS, wa + kk, ok && row_a);
+      cp_async_16<false>(slot + (2 * h + 1) * THREADS, wb + kk, ok && row_b);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        uint4 bb = ldg_keep(xr[nt] + ks);
-        if (!ok) bb = zero;
-        mma(acc[nt], al.x, ah.x, al.y, ah.y, bb.x, bb.y);
-        mma(acc[nt], al.z, ah.z, al.w, ah.w, bb.z, bb.w);
+        uint4* xs = slot + (4 + (nt * 2 + h) * XP) * THREADS;
+        cp_async_16<true>(xs, xr[nt] + kk, ok && tok_ok[nt]);
+        if (PRO == PRO_SILU) cp_async_16<true>(xs + THREADS, xr[nt] + K + kk, ok && tok_ok[nt]);
+      }
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < my_chunks) issue(s);
+    cp_async_commit();
+  }
+  for (int i = 0; i < my_chunks; ++i) {
+    if (i + STAGES - 1 < my_chunks) issue(i + STAGES - 1);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();  // this thread's copies of chunk i have landed; only it reads them
+    const uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 a_lo = slot[(2 * h) * THREADS], a_hi = slot[(2 * h + 1) * THREADS];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4* xs = slot + (4 + (nt * 2 + h) * XP) * THREADS;
+        uint4 b = xs[0];
+        if (PRO == PRO_SILU) b = silu_gate8(b, xs[THREADS]);
+        mma(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+        mma(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
       }
     }
   }
@@ -123,40 +181,89 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     red[warp][r + 8][nt * 8 + 2 * c + 1] = acc[nt][3];
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < ROWS * NT * 8; i += WARPS * 32) {
-    const int tok = i / ROWS, row = i - tok * ROWS;  // consecutive threads write consecutive columns of y
-    if (tok < M && n0 + row < N) {
-      float s = 0.f;
+  auto total = [&](int row, int tok) {
+    float s = 0.f;
 #pragma unroll
-      for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][tok];
-      y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(s);
+    for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][tok];
+    return s;
+  };
+  if (EPI == EPI_PLAIN) {
+    for (int i = tid; i < ROWS * NT * 8; i += THREADS) {
+      const int tok = i / ROWS, row = i - tok * ROWS;  // consecutive threads write consecutive columns of y
+      if (tok < M && n0 + row < N) y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(total(row, tok));
+    }
+  } else {
+    // the block's 16 rows are 8 adjacent pairs of one head of q, k or v
+    const int hd = qkv.head_dim, q_width = qkv.n_heads * hd, kv_width = qkv.n_kv_heads * hd;
+    for (int i = tid; i < (ROWS / 2) * NT * 8; i += THREADS) {
+      const int tok = i / (ROWS / 2), pr = i - tok * (ROWS / 2);
+      const int n = n0 + 2 * pr;
+      if (tok >= M || n >= N) continue;
+      const int slot_req = qkv.req[tok];
+      if (slot_req < 0) continue;  // padding lane
+      float re = total(2 * pr, tok), im = total(2 * pr + 1, tok);
+      const int p = qkv.pos[tok];
+      const bool is_v = n >= q_width + kv_width;
+      if (!is_v) {
+        // the product is rounded to bfloat16 before the rotation, as a separate kernel would see it
+        re = __bfloat162float(__float2bfloat16_rn(re));
+        im = __bfloat162float(__float2bfloat16_rn(im));
+        float s = 0.f, cs = 1.f;
+        if (qkv.freqs != nullptr) sincosf((float)p * qkv.freqs[(n % hd) >> 1], &s, &cs);
+        const float rr = re * cs - im * s, ii = im * cs + re * s;
+        re = rr;
+        im = ii;
+      }
+      const __nv_bfloat162 out2 = __floats2bfloat162_rn(re, im);
+      if (n < q_width) {
+        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(y) + (size_t)tok * ldy + n) = out2;
+        continue;
+      }
+      const int col = n - q_width - (is_v ? kv_width : 0);
+      const int g = col / hd, d = col - g * hd;
+      const int logical = p / qkv.page_size;
+      const int page = logical < qkv.table_width ? qkv.block_table[(size_t)slot_req * qkv.table_width + logical] : -1;
+      if (page < 0 || page >= qkv.n_pages) {
+        if (qkv.status) atomicOr(qkv.status, FG_STATUS_BAD_PAGE);
+        continue;
+      }
+      const size_t dst =
+          (((size_t)page * qkv.n_kv_heads + g) * qkv.page_size + (p - logical * qkv.page_size)) * hd + d;
+      *reinterpret_cast<__nv_bfloat162*>((is_v ? qkv.v_pages : qkv.k_pages) + dst) = out2;
     }
   }
 }
 
-template <typename TO>
+template <int NT, typename TO, int PRO, int EPI>
+int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
+               const QkvEpilogue& qkv, cudaStream_t stream) {
+  auto kern = gemm_skinny_kernel<NT, TO, PRO, EPI>;
+  constexpr size_t smem = Ring<NT, PRO>::BYTES;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_gemm_skinny: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  kern<<<(N + ROWS - 1) / ROWS, THREADS, smem, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
+                                                         ldw, (TO*)y, ldy, M, N, K, qkv);
+  return 0;
+}
+
+template <typename TO, int PRO, int EPI>
 int launch(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
-           cudaStream_t stream) {
-  const int grid = (N + ROWS - 1) / ROWS;
-  const auto* xp = (const __nv_bfloat16*)x;
-  const auto* wp = (const __nv_bfloat16*)w;
-  // Few blocks (a small N): 16 warps a block, so that enough loads are in flight
-  // on every SM; the split of K only depends on N and K, never on the batch.
-  const bool wide = grid < 4 * 148 && K >= 16 * CHUNK;
-#define FG_SKINNY(NT)                                                                                       \
-  do {                                                                                                      \
-    if (wide)                                                                                               \
-      gemm_skinny_kernel<NT, TO, 16><<<grid, 16 * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K); \
-    else                                                                                                    \
-      gemm_skinny_kernel<NT, TO, 8><<<grid, 8 * 32, 0, stream>>>(xp, ldx, wp, ldw, (TO*)y, ldy, M, N, K);   \
-  } while (0)
-  if (M <= 8)
-    FG_SKINNY(1);
-  else if (M <= 16)
-    FG_SKINNY(2);
-  else
-    FG_SKINNY(4);
-#undef FG_SKINNY
+           const QkvEpilogue& qkv, cudaStream_t stream) {
+  if (M <= 8) return launch_one<1, TO, PRO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  if (M <= 16) return launch_one<2, TO, PRO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  return launch_one<4, TO, PRO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+}
+
+int check_common(const char* name, const void* x, int ldx, const void* w, int ldw, int ldy, int M, int N, int K,
+                 int x_width) {
+  FG_CHECK_ARG(M <= 32, "%s: M=%d exceeds 32", name, M);
+  FG_CHECK_ARG(K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldx >= x_width && ldw >= K && ldy >= N,
+               "%s: K=%d and the row strides (%d, %d) must be multiples of 8", name, K, ldx, ldw);
+  FG_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "%s: x and w must be 16-byte aligned", name);
   return 0;
 }
 
@@ -169,17 +276,48 @@ extern "C" int fg_gemm_skinny_max_m() { return 32; }
 extern "C" int fg_gemm_skinny_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
                                    int out_dtype, int M, int N, int K, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  FG_CHECK_ARG(M <= 32, "fg_gemm_skinny_bf16: M=%d exceeds 32", M);
-  FG_CHECK_ARG(K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldx >= K && ldw >= K && ldy >= N,
-               "fg_gemm_skinny_bf16: K=%d and the row strides (%d, %d) must be multiples of 8", K, ldx, ldw);
-  FG_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0,
-               "fg_gemm_skinny_bf16: x and w must be 16-byte aligned");
+  if (check_common("fg_gemm_skinny_bf16", x, ldx, w, ldw, ldy, M, N, K, K)) return -1;
+  QkvEpilogue none{};
   if (out_dtype == FG_BF16)
-    launch<__nv_bfloat16>(x, ldx, w, ldw, y, ldy, M, N, K, stream);
+    launch<__nv_bfloat16, PRO_PLAIN, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
   else if (out_dtype == FG_F32)
-    launch<float>(x, ldx, w, ldw, y, ldy, M, N, K, stream);
+    launch<float, PRO_PLAIN, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
   else
     FG_CHECK_ARG(false, "fg_gemm_skinny_bf16: bad output dtype %d", out_dtype);
   FG_CHECK_LAUNCH("fg_gemm_skinny_bf16");
+  return 0;
+}
+
+// y[M, N] = (silu(x[:, :K]) * x[:, K:2K]) * W[N, K]^T for x = [gate | up] of width 2K.
+extern "C" int fg_gemm_skinny_silu_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
+                                        int M, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (check_common("fg_gemm_skinny_silu_bf16", x, ldx, w, ldw, ldy, M, N, K, 2 * K)) return -1;
+  QkvEpilogue none{};
+  launch<__nv_bfloat16, PRO_SILU, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
+  FG_CHECK_LAUNCH("fg_gemm_skinny_silu_bf16");
+  return 0;
+}
+
+// The fused projection of queries, keys and values for single tokens and small
+// batches: w = [wq; wk; wv] with N = (n_heads + 2 n_kv_heads) * head_dim.  Rotated
+// queries go to y[:, :n_heads*head_dim]; rotated keys and the values go to the
+// pages of (req[t], pos[t]).  freqs may be null (no rotation).
+extern "C" int fg_gemm_skinny_qkv_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
+                                       int M, int K, const int* pos, const int* req, const float* freqs,
+                                       void* k_pages, void* v_pages, const int* block_table, int table_width,
+                                       int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim,
+                                       int* status, cudaStream_t stream) {
+  const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+  if (M == 0) return 0;
+  if (check_common("fg_gemm_skinny_qkv_bf16", x, ldx, w, ldw, ldy, M, n_heads * head_dim, K, K)) return -1;
+  FG_CHECK_ARG(head_dim % 16 == 0, "fg_gemm_skinny_qkv_bf16: head size %d is not a multiple of 16", head_dim);
+  FG_CHECK_ARG(ldy % 2 == 0 && ((uintptr_t)y & 3) == 0 && ((uintptr_t)k_pages & 3) == 0 &&
+                   ((uintptr_t)v_pages & 3) == 0,
+               "fg_gemm_skinny_qkv_bf16: outputs must be 4-byte aligned");
+  QkvEpilogue qkv{pos, req, freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width,
+                  page_size, n_pages, n_heads, n_kv_heads, head_dim, status};
+  launch<__nv_bfloat16, PRO_PLAIN, EPI_QKV>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  FG_CHECK_LAUNCH("fg_gemm_skinny_qkv_bf16");
   return 0;
 }

@@ -46,6 +46,9 @@ _CORE_SIGNATURES = {
     "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+    "fg_gemm_skinny_silu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
+    "fg_gemm_skinny_qkv_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                                _P, _P],
     "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
     "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
     "fg_make_kv_tensor_map": [_P, _P, _I, _I, _I, _I, _I, _I],
@@ -250,6 +253,41 @@ class Ops:
             out.copy_(res)
             return out
         return res
+
+    def _skinny_ok(self, x: torch.Tensor, w: torch.Tensor, k: int) -> bool:
+        return (x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_M and k % 8 == 0
+                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def linear_silu_gate(self, x13: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+        """``(silu(x13[:, :F]) * x13[:, F:]) @ w.T`` in one kernel for a few
+        tokens; ``None`` when the shapes do not allow it (the caller then runs
+        the gate and the product separately)."""
+        m, two_f = x13.shape
+        n, f = w.shape
+        if two_f != 2 * f or not self._skinny_ok(x13, w, f):
+            return None
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x13.device)
+        _check(self.lib, self.lib.fg_gemm_skinny_silu_bf16(
+            _ptr(x13), x13.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), m, n, f, _stream()))
+        return out
+
+    def qkv_rope_write(self, x, wqkv, pos, req, freqs, memory, n_heads: int, n_kv_heads: int,
+                       head_dim: int) -> Optional[torch.Tensor]:
+        """Queries, keys and values of a few tokens in one kernel: the product
+        against ``[wq; wk; wv]``, the rotation, and the write of keys and
+        values into their pages.  Returns the rotated queries [T, heads*head_dim],
+        or ``None`` when the shapes do not allow it."""
+        m, k = x.shape
+        if not self._skinny_ok(x, wqkv, k) or head_dim % 16:
+            return None
+        q = torch.empty((m, n_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+        _check(self.lib, self.lib.fg_gemm_skinny_qkv_bf16(
+            _ptr(x), x.stride(0), _ptr(wqkv), wqkv.stride(0), _ptr(q), q.stride(0), m, k,
+            _ptr(pos), _ptr(req), _ptr(freqs), _ptr(memory.k_pages), _ptr(memory.v_pages),
+            _ptr(memory.block_table), memory.block_table.shape[1], memory.page_size,
+            memory.k_pages.shape[0], n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
+        return q
 
     def silu_gate(self, x13: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         n, two_f = x13.shape

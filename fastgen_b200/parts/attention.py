@@ -68,19 +68,25 @@ class GQAAttention(Mixer):
     def forward(self, x, ctx, memory):
         p, ops = self.params, self.ops
         t = x.shape[0]
-        if memory.writes:
-            qkv = ops.linear(x, self.wqkv)
-            q = qkv[:, : self.q_width]
-            k = qkv[:, self.q_width : self.q_width + self.kv_width]
-            v = qkv[:, self.q_width + self.kv_width :]
-        else:
-            # this run reads another run's cache: only queries are needed
-            q = ops.linear(x, self.wqkv[: self.q_width])
-            k = v = None
-        ops.rope_kv_write(
-            q, k, v, ctx.pos, ctx.req, self.freqs, memory.k_pages, memory.v_pages,
-            memory.block_table, memory.page_size, p.n_heads, p.n_kv_heads, p.head_dim,
-        )
+        q = None
+        if memory.writes and x.dtype == torch.bfloat16:
+            # a few tokens: projection, rotation and page write in one kernel
+            q = ops.qkv_rope_write(x, self.wqkv, ctx.pos, ctx.req, self.freqs, memory,
+                                   p.n_heads, p.n_kv_heads, p.head_dim)
+        if q is None:
+            if memory.writes:
+                qkv = ops.linear(x, self.wqkv)
+                q = qkv[:, : self.q_width]
+                k = qkv[:, self.q_width : self.q_width + self.kv_width]
+                v = qkv[:, self.q_width + self.kv_width :]
+            else:
+                # this run reads another run's cache: only queries are needed
+                q = ops.linear(x, self.wqkv[: self.q_width])
+                k = v = None
+            ops.rope_kv_write(
+                q, k, v, ctx.pos, ctx.req, self.freqs, memory.k_pages, memory.v_pages,
+                memory.block_table, memory.page_size, p.n_heads, p.n_kv_heads, p.head_dim,
+            )
         o = torch.empty((t, self.q_width), dtype=x.dtype, device=x.device)
         ops.attention(
             q, o, memory, ctx, p.n_heads, p.n_kv_heads, p.head_dim, p.window, self.scale,

@@ -125,6 +125,59 @@ def test_gemm_skinny(ops16, m, n, k):
     assert torch.equal(ops16.linear(wide[:, 8 : 8 + k], w, out_dtype=torch.float32), out32)
 
 
+@pytest.mark.parametrize("m", [1, 8, 11, 32])
+@pytest.mark.parametrize("n,f", [(192, 512), (200, 328), (4096, 14336), (72, 8)])
+def test_gemm_skinny_silu_gate(ops16, m, n, f):
+    """The down projection with the gate computed in its prologue, against gate-then-product."""
+    g = torch.Generator().manual_seed(m * n + f)
+    x13 = (torch.randn(m, 2 * f, generator=g) * 1.5).to(DEV, torch.bfloat16)
+    w = (torch.randn(n, f, generator=g) / math.sqrt(f)).to(DEV, torch.bfloat16)
+    out = ops16.linear_silu_gate(x13, w)
+    assert out is not None and out.dtype == torch.bfloat16
+    xd = x13.double()
+    gate = (xd[:, :f] * torch.sigmoid(xd[:, :f]) * xd[:, f:]).to(torch.bfloat16).double()  # rounded once, as the operand is
+    ref = gate @ w.double().T
+    err = (out.double() - ref).abs()
+    assert bool((err <= ref.abs() * 2.0 ** -8 + 2e-3).all()), float(err.max())
+    assert ops16.linear_silu_gate(x13[:, : 2 * f - 8], w) is None  # shapes that do not fit are declined
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 20])
+@pytest.mark.parametrize("hq,hkv,hd,page,dim", [(4, 1, 16, 8, 64), (6, 3, 32, 16, 192), (6, 2, 48, 8, 200), (32, 8, 128, 64, 4096)])
+def test_gemm_skinny_qkv_rope_write(ops16, m, hq, hkv, hd, page, dim):
+    """Projection + rotation + page write in one kernel, against the three separate kernels."""
+    from fastgen_b200.cache import LayerMemory
+    g = torch.Generator().manual_seed(m + hd)
+    x = torch.randn(m, dim, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn((hq + 2 * hkv) * hd, dim, generator=g) / math.sqrt(dim)).to(DEV, torch.bfloat16)
+    freqs = pl.rope_freqs(hd, 10000.0, None).to(DEV)
+    n_pages, width = 40, 8
+    table = torch.full((m + 1, width), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    pos = torch.tensor([(7 * i + page - 1) % (page * width) for i in range(m)], dtype=torch.int32)
+    req = torch.tensor([(i + 1) % (m + 1) for i in range(m)], dtype=torch.int32)
+    req[m // 2] = -1 if m > 2 else req[m // 2]   # a padding lane
+    for i in range(m):
+        if req[i] >= 0:
+            table[req[i], pos[i] // page] = perm.pop()
+    mems = []
+    for _ in range(2):
+        kp = torch.zeros(n_pages, hkv, page, hd, dtype=torch.bfloat16, device=DEV)
+        mems.append(LayerMemory(k_pages=kp, v_pages=torch.zeros_like(kp), block_table=table.to(DEV), page_size=page))
+    pos, req = pos.to(DEV), req.to(DEV)
+    q = ops16.qkv_rope_write(x, w, pos, req, freqs, mems[0], hq, hkv, hd)
+    assert q is not None
+    qkv = ops16.linear(x, w)
+    ops16.rope_kv_write(qkv[:, : hq * hd], qkv[:, hq * hd : (hq + hkv) * hd], qkv[:, (hq + hkv) * hd :], pos, req,
+                        freqs, mems[1].k_pages, mems[1].v_pages, mems[1].block_table, page, hq, hkv, hd)
+    ops16.check_status()
+    live = (req >= 0).cpu()
+    assert torch.allclose(q[live].float(), qkv[live][:, : hq * hd].float(), rtol=2e-2, atol=2e-2)
+    assert torch.allclose(mems[0].k_pages.float(), mems[1].k_pages.float(), rtol=2e-2, atol=2e-2)
+    assert torch.allclose(mems[0].v_pages.float(), mems[1].v_pages.float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(mems[0].k_pages == 0, mems[1].k_pages == 0)   # the same slots were written, no others
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("ffn", [176, 331, 14336])
 def test_silu_gate(ops32, dtype, ffn):
