@@ -14,9 +14,10 @@
 // nothing but K.
 //
 // Two fused variants serve the decode step:
-//  * prologue "SiLU gate": x is [gate | up] of width 2K and the operand is
-//    silu(gate) * up computed on the fly (the feed-forward's down projection,
-//    fastgen/forward.py:495-496);
+//  * epilogue "SwiGLU": W holds gate and up rows interleaved in blocks of 8 (rows
+//    16b..16b+7 gate, 16b+8..16b+15 up of features 8b..8b+7), so a block's 16 rows
+//    are gate and up of the same 8 features and it writes silu(gate) * up
+//    (fastgen/forward.py:491-495) -- the [gate | up] intermediate never exists;
 //  * epilogue "QKV": the 16 output rows are 8 adjacent pairs of one head; they are
 //    rotated by the token's position (fastgen/kernels/rope.py:77-89), queries go
 //    to y, keys and values straight into their cache pages
@@ -33,8 +34,7 @@ constexpr int CHUNK = 64;  // k elements per warp step
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 
-enum { PRO_PLAIN = 0, PRO_SILU = 1 };
-enum { EPI_PLAIN = 0, EPI_QKV = 1 };
+enum { EPI_PLAIN = 0, EPI_QKV = 1, EPI_SWIGLU = 2 };
 
 struct QkvEpilogue {
   const int* pos;
@@ -77,35 +77,20 @@ __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// silu(g) * u on eight bfloat16 values, float32 arithmetic, one rounding
-__device__ __forceinline__ uint4 silu_gate8(uint4 g4, uint4 u4) {
-  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
-  uint4 o4;
-  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-    o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
-  }
-  return o4;
-}
-
 // 16-byte pieces a thread copies per chunk (4 of W, the rest of x), ring depth, ring size
-template <int NT, int PRO>
+template <int NT>
 struct Ring {
-  static constexpr int PIECES = 4 + 2 * NT * (PRO == PRO_SILU ? 2 : 1);
-  static constexpr int STAGES = PIECES <= 8 ? 4 : (PIECES <= 12 ? 3 : 2);
+  static constexpr int PIECES = 4 + 2 * NT;
+  static constexpr int STAGES = NT == 1 ? 4 : (NT == 2 ? 3 : 2);  // 96 KiB a block: two blocks an SM
   static constexpr size_t BYTES = (size_t)STAGES * PIECES * THREADS * 16;
 };
 
-template <int NT, typename TO, int PRO, int EPI>
+template <int NT, typename TO, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
                    TO* __restrict__ y, int ldy, int M, int N, int K, QkvEpilogue qkv) {
-  constexpr int PIECES = Ring<NT, PRO>::PIECES;
-  constexpr int STAGES = Ring<NT, PRO>::STAGES;
-  constexpr int XP = PRO == PRO_SILU ? 2 : 1;  // x pieces per (token tile, half): gate and up, or one
+  constexpr int PIECES = Ring<NT>::PIECES;
+  constexpr int STAGES = Ring<NT>::STAGES;
   extern __shared__ __align__(16) unsigned char ring_raw[];
   uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [STAGES][PIECES][THREADS]
   __shared__ float red[WARPS][ROWS][NT * 8];
@@ -143,9 +128,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
       cp_async_16<false>(slot + (2 * h + 1) * THREADS, wb + kk, ok && row_b);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        uint4* xs = slot + (4 + (nt * 2 + h) * XP) * THREADS;
-        cp_async_16<true>(xs, xr[nt] + kk, ok && tok_ok[nt]);
-        if (PRO == PRO_SILU) cp_async_16<true>(xs + THREADS, xr[nt] + K + kk, ok && tok_ok[nt]);
+        cp_async_16<true>(slot + (4 + nt * 2 + h) * THREADS, xr[nt] + kk, ok && tok_ok[nt]);
       }
     }
   };
@@ -165,9 +148,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
       const uint4 a_lo = slot[(2 * h) * THREADS], a_hi = slot[(2 * h + 1) * THREADS];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const uint4* xs = slot + (4 + (nt * 2 + h) * XP) * THREADS;
-        uint4 b = xs[0];
-        if (PRO == PRO_SILU) b = silu_gate8(b, xs[THREADS]);
+        const uint4 b = slot[(4 + nt * 2 + h) * THREADS];
         mma(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
         mma(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
       }
@@ -191,6 +172,17 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     for (int i = tid; i < ROWS * NT * 8; i += THREADS) {
       const int tok = i / ROWS, row = i - tok * ROWS;  // consecutive threads write consecutive columns of y
       if (tok < M && n0 + row < N) y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(total(row, tok));
+    }
+  } else if (EPI == EPI_SWIGLU) {
+    // rows 0..7 are the gates and rows 8..15 the ups of features n0/2 .. n0/2+7
+    for (int i = tid; i < 8 * NT * 8; i += THREADS) {
+      const int tok = i / 8, f = i - tok * 8;
+      if (tok < M && n0 + 8 + f < N) {
+        const float g = total(f, tok), u = total(f + 8, tok);
+        // both are rounded to bfloat16 first, as a separate gate kernel would see them
+        const float gr = __bfloat162float(__float2bfloat16_rn(g)), ur = __bfloat162float(__float2bfloat16_rn(u));
+        y[(size_t)tok * ldy + n0 / 2 + f] = from_f32<TO>(gr / (1.f + expf(-gr)) * ur);
+      }
     }
   } else {
     // the block's 16 rows are 8 adjacent pairs of one head of q, k or v
@@ -234,11 +226,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
   }
 }
 
-template <int NT, typename TO, int PRO, int EPI>
+template <int NT, typename TO, int EPI>
 int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
                const QkvEpilogue& qkv, cudaStream_t stream) {
-  auto kern = gemm_skinny_kernel<NT, TO, PRO, EPI>;
-  constexpr size_t smem = Ring<NT, PRO>::BYTES;
+  auto kern = gemm_skinny_kernel<NT, TO, EPI>;
+  constexpr size_t smem = Ring<NT>::BYTES;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -250,12 +242,12 @@ int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
   return 0;
 }
 
-template <typename TO, int PRO, int EPI>
+template <typename TO, int EPI>
 int launch(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
            const QkvEpilogue& qkv, cudaStream_t stream) {
-  if (M <= 8) return launch_one<1, TO, PRO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
-  if (M <= 16) return launch_one<2, TO, PRO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
-  return launch_one<4, TO, PRO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  if (M <= 8) return launch_one<1, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  if (M <= 16) return launch_one<2, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  return launch_one<4, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
 }
 
 int check_common(const char* name, const void* x, int ldx, const void* w, int ldw, int ldy, int M, int N, int K,
@@ -279,23 +271,25 @@ extern "C" int fg_gemm_skinny_bf16(const void* x, int ldx, const void* w, int ld
   if (check_common("fg_gemm_skinny_bf16", x, ldx, w, ldw, ldy, M, N, K, K)) return -1;
   QkvEpilogue none{};
   if (out_dtype == FG_BF16)
-    launch<__nv_bfloat16, PRO_PLAIN, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
+    launch<__nv_bfloat16, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
   else if (out_dtype == FG_F32)
-    launch<float, PRO_PLAIN, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
+    launch<float, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
   else
     FG_CHECK_ARG(false, "fg_gemm_skinny_bf16: bad output dtype %d", out_dtype);
   FG_CHECK_LAUNCH("fg_gemm_skinny_bf16");
   return 0;
 }
 
-// y[M, N] = (silu(x[:, :K]) * x[:, K:2K]) * W[N, K]^T for x = [gate | up] of width 2K.
-extern "C" int fg_gemm_skinny_silu_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
-                                        int M, int N, int K, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
-  if (check_common("fg_gemm_skinny_silu_bf16", x, ldx, w, ldw, ldy, M, N, K, 2 * K)) return -1;
+// y[M, F] = silu(x W1^T) * (x W3^T) for w = W1 and W3 interleaved in blocks of 8 rows
+// ([2F, K]: rows 16b..16b+7 are rows 8b..8b+7 of W1, rows 16b+8..16b+15 those of W3).
+extern "C" int fg_gemm_skinny_swiglu_bf16(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
+                                          int M, int F, int K, cudaStream_t stream) {
+  if (M == 0 || F == 0) return 0;
+  FG_CHECK_ARG(F % 8 == 0, "fg_gemm_skinny_swiglu_bf16: the feed-forward width %d is not a multiple of 8", F);
+  if (check_common("fg_gemm_skinny_swiglu_bf16", x, ldx, w, ldw, ldy, M, F, K, K)) return -1;
   QkvEpilogue none{};
-  launch<__nv_bfloat16, PRO_SILU, EPI_PLAIN>(x, ldx, w, ldw, y, ldy, M, N, K, none, stream);
-  FG_CHECK_LAUNCH("fg_gemm_skinny_silu_bf16");
+  launch<__nv_bfloat16, EPI_SWIGLU>(x, ldx, w, ldw, y, ldy, M, 2 * F, K, none, stream);
+  FG_CHECK_LAUNCH("fg_gemm_skinny_swiglu_bf16");
   return 0;
 }
 
@@ -317,7 +311,7 @@ extern "C" int fg_gemm_skinny_qkv_bf16(const void* x, int ldx, const void* w, in
                "fg_gemm_skinny_qkv_bf16: outputs must be 4-byte aligned");
   QkvEpilogue qkv{pos, req, freqs, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table, table_width,
                   page_size, n_pages, n_heads, n_kv_heads, head_dim, status};
-  launch<__nv_bfloat16, PRO_PLAIN, EPI_QKV>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+  launch<__nv_bfloat16, EPI_QKV>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
   FG_CHECK_LAUNCH("fg_gemm_skinny_qkv_bf16");
   return 0;
 }

@@ -42,11 +42,11 @@ _P, _I, _F = c_void_p, c_int, c_float
 _CORE_SIGNATURES = {
     "fg_embedding": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "fg_rmsnorm": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P],
-    "fg_silu_gate": [_P, _P, _I, _I, _I, _P],
+    "fg_silu_gate": [_P, _P, _I, _I, _I, _I, _P],
     "fg_rope_kv_write": [_P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "fg_gemm_f32_nt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "fg_gemm_skinny_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
-    "fg_gemm_skinny_silu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
+    "fg_gemm_skinny_swiglu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "fg_gemm_skinny_qkv_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                                 _P, _P],
     "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
@@ -65,7 +65,7 @@ _ATTN_SIGNATURES = {
                                      _F, _P, ctypes.c_longlong, _I, _P, _P],
 }
 
-SKINNY_MAX_M = 32     # most tokens the weight-streaming product takes
+SKINNY_MAX_M = 8      # most tokens the weight-streaming product is used for (it takes up to 32)
 SIMT_ROWS = 16       # query rows per block of the float32 attention kernel
 PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
 PREFILL_TMA_ROWS = 128  # ... of the bfloat16 prompt kernel with tiled TMA loads
@@ -259,17 +259,18 @@ class Ops:
                 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
-    def linear_silu_gate(self, x13: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
-        """``(silu(x13[:, :F]) * x13[:, F:]) @ w.T`` in one kernel for a few
-        tokens; ``None`` when the shapes do not allow it (the caller then runs
-        the gate and the product separately)."""
-        m, two_f = x13.shape
-        n, f = w.shape
-        if two_f != 2 * f or not self._skinny_ok(x13, w, f):
+    def linear_swiglu(self, x: torch.Tensor, w13: torch.Tensor) -> Optional[torch.Tensor]:
+        """``silu(x @ w1.T) * (x @ w3.T)`` in one kernel for a few tokens, for
+        ``w13`` that holds w1 and w3 interleaved in blocks of 8 rows; ``None``
+        when the shapes do not allow it (the caller then runs the product and
+        the gate separately)."""
+        m, k = x.shape
+        f = w13.shape[0] // 2
+        if f % 8 or not self._skinny_ok(x, w13, k):
             return None
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=x13.device)
-        _check(self.lib, self.lib.fg_gemm_skinny_silu_bf16(
-            _ptr(x13), x13.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), m, n, f, _stream()))
+        out = torch.empty((m, f), dtype=torch.bfloat16, device=x.device)
+        _check(self.lib, self.lib.fg_gemm_skinny_swiglu_bf16(
+            _ptr(x), x.stride(0), _ptr(w13), w13.stride(0), _ptr(out), out.stride(0), m, f, k, _stream()))
         return out
 
     def qkv_rope_write(self, x, wqkv, pos, req, freqs, memory, n_heads: int, n_kv_heads: int,
@@ -289,10 +290,13 @@ class Ops:
             memory.k_pages.shape[0], n_heads, n_kv_heads, head_dim, _ptr(self.status), _stream()))
         return q
 
-    def silu_gate(self, x13: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def silu_gate(self, x13: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+        """``silu(gate) * up`` for ``x13`` holding gate and up as halves
+        (``interleave=0``) or interleaved in blocks of 8 columns (``8``)."""
         n, two_f = x13.shape
         assert x13.is_contiguous() and out.is_contiguous() and out.shape == (n, two_f // 2)
-        _check(self.lib, self.lib.fg_silu_gate(_ptr(x13), _ptr(out), _code(x13.dtype), n, two_f // 2, _stream()))
+        _check(self.lib, self.lib.fg_silu_gate(_ptr(x13), _ptr(out), _code(x13.dtype), n, two_f // 2,
+                                               interleave, _stream()))
         return out
 
     def rope_kv_write(self, q, k, v, pos, req, freqs, k_pages, v_pages, block_table,

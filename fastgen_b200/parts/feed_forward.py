@@ -28,19 +28,29 @@ class SwiGLU(FeedForward):
     def bind(self, tensors, ops) -> None:
         self.ops = ops
         dt = ops.act_dtype
-        self.w13 = torch.cat([tensors["w1"], tensors["w3"]], dim=0).to(dt).contiguous()
+        w1, w3 = tensors["w1"], tensors["w3"]
+        f, d = w1.shape
+        # gate and up rows interleaved in blocks of 8, so that 16 consecutive rows of
+        # the fused weight are gate and up of the same 8 features (what the decode
+        # kernel's epilogue needs); widths that are no multiple of 8 keep two halves
+        self.interleave = 8 if f % 8 == 0 else 0
+        if self.interleave:
+            w13 = torch.stack([w1.view(f // 8, 8, d), w3.view(f // 8, 8, d)], dim=1).reshape(2 * f, d)
+        else:
+            w13 = torch.cat([w1, w3], dim=0)
+        self.w13 = w13.to(dt).contiguous()
         self.w2 = tensors["w2"].to(dt).contiguous()
 
     def forward(self, x, ctx):
         ops = self.ops
-        x13 = ops.linear(x, self.w13)
-        if x.dtype == torch.bfloat16:
-            # a few tokens: the gate is computed inside the down projection
-            y = ops.linear_silu_gate(x13, self.w2)
-            if y is not None:
-                return y
-        g = torch.empty((x.shape[0], self.params.ffn_dim), dtype=x.dtype, device=x.device)
-        ops.silu_gate(x13, g)
+        g = None
+        if x.dtype == torch.bfloat16 and self.interleave:
+            # a few tokens: product and gate in one kernel, the [gate | up] rows never exist
+            g = ops.linear_swiglu(x, self.w13)
+        if g is None:
+            x13 = ops.linear(x, self.w13)
+            g = torch.empty((x.shape[0], self.params.ffn_dim), dtype=x.dtype, device=x.device)
+            ops.silu_gate(x13, g, self.interleave)
         return ops.linear(g, self.w2)
 
 

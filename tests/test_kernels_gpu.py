@@ -105,11 +105,15 @@ def test_linear_bf16(ops16):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("n,k", [(320, 192), (331, 200), (4096, 4096), (1000, 14336), (17, 72), (64, 8)])
-def test_gemm_skinny(ops16, m, n, k):
+def test_gemm_skinny(ops16, request, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
     w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(DEV, torch.bfloat16)
     ref = x.double() @ w.double().T
+    from fastgen_b200.csrc import ops as O
+    monkey = O.SKINNY_MAX_M
+    O.SKINNY_MAX_M = 32  # the kernel takes up to 32 tokens; the engine uses it for fewer
+    request.addfinalizer(lambda: setattr(O, "SKINNY_MAX_M", monkey))
     out32 = ops16.linear(x, w, out_dtype=torch.float32)
     assert out32.dtype == torch.float32
     assert torch.allclose(out32.double(), ref, rtol=1e-4, atol=2e-4), float((out32.double() - ref).abs().max())
@@ -126,20 +130,32 @@ def test_gemm_skinny(ops16, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 8, 11, 32])
-@pytest.mark.parametrize("n,f", [(192, 512), (200, 328), (4096, 14336), (72, 8)])
-def test_gemm_skinny_silu_gate(ops16, m, n, f):
-    """The down projection with the gate computed in its prologue, against gate-then-product."""
-    g = torch.Generator().manual_seed(m * n + f)
-    x13 = (torch.randn(m, 2 * f, generator=g) * 1.5).to(DEV, torch.bfloat16)
-    w = (torch.randn(n, f, generator=g) / math.sqrt(f)).to(DEV, torch.bfloat16)
-    out = ops16.linear_silu_gate(x13, w)
-    assert out is not None and out.dtype == torch.bfloat16
-    xd = x13.double()
-    gate = (xd[:, :f] * torch.sigmoid(xd[:, :f]) * xd[:, f:]).to(torch.bfloat16).double()  # rounded once, as the operand is
-    ref = gate @ w.double().T
-    err = (out.double() - ref).abs()
-    assert bool((err <= ref.abs() * 2.0 ** -8 + 2e-3).all()), float(err.max())
-    assert ops16.linear_silu_gate(x13[:, : 2 * f - 8], w) is None  # shapes that do not fit are declined
+@pytest.mark.parametrize("f,k", [(512, 192), (328, 200), (14336, 4096), (8, 72)])
+def test_gemm_skinny_swiglu(ops16, m, f, k):
+    """Gate/up product with the gate in its epilogue, against product-then-gate."""
+    g = torch.Generator().manual_seed(m * k + f)
+    x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
+    w1 = (torch.randn(f, k, generator=g) * 2 / math.sqrt(k)).to(torch.bfloat16)
+    w3 = (torch.randn(f, k, generator=g) * 2 / math.sqrt(k)).to(torch.bfloat16)
+    w13 = torch.stack([w1.view(f // 8, 8, k), w3.view(f // 8, 8, k)], dim=1).reshape(2 * f, k).to(DEV)
+    from fastgen_b200.csrc import ops as O
+    old, O.SKINNY_MAX_M = O.SKINNY_MAX_M, 32
+    try:
+        out = ops16.linear_swiglu(x, w13)
+    finally:
+        O.SKINNY_MAX_M = old
+    assert out is not None and out.shape == (m, f)
+    x1 = (x.double().cpu() @ w1.double().T).to(torch.bfloat16).double()   # each product rounded once
+    x3 = (x.double().cpu() @ w3.double().T).to(torch.bfloat16).double()
+    ref = x1 * torch.sigmoid(x1) * x3
+    err = (out.double().cpu() - ref).abs()
+    # one bfloat16 ulp of either product moves the result by about 2^-7 of it
+    assert bool((err <= ref.abs() * 2.0 ** -6 + 2e-2).all()), float(err.max())
+    # the separate gate kernel reads the same interleaved layout
+    x13 = ops16.linear(x, w13)
+    out2 = torch.empty(m, f, dtype=torch.bfloat16, device=DEV)
+    ops16.silu_gate(x13, out2, 8)
+    assert torch.allclose(out2.float(), out.float(), rtol=3e-2, atol=3e-2)
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 20])
@@ -165,7 +181,12 @@ def test_gemm_skinny_qkv_rope_write(ops16, m, hq, hkv, hd, page, dim):
         kp = torch.zeros(n_pages, hkv, page, hd, dtype=torch.bfloat16, device=DEV)
         mems.append(LayerMemory(k_pages=kp, v_pages=torch.zeros_like(kp), block_table=table.to(DEV), page_size=page))
     pos, req = pos.to(DEV), req.to(DEV)
-    q = ops16.qkv_rope_write(x, w, pos, req, freqs, mems[0], hq, hkv, hd)
+    from fastgen_b200.csrc import ops as O
+    old, O.SKINNY_MAX_M = O.SKINNY_MAX_M, 32
+    try:
+        q = ops16.qkv_rope_write(x, w, pos, req, freqs, mems[0], hq, hkv, hd)
+    finally:
+        O.SKINNY_MAX_M = old
     assert q is not None
     qkv = ops16.linear(x, w)
     ops16.rope_kv_write(qkv[:, : hq * hd], qkv[:, hq * hd : (hq + hkv) * hd], qkv[:, (hq + hkv) * hd :], pos, req,
