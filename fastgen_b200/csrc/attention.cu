@@ -198,13 +198,14 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
     attr_set = true;
   }
   dim3 grid(max_splits, n_kv_heads, n_seqs);
-  kern<<<grid, THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, block_table,
-                                        table_width, page_size, n_pages, pos, seq_req, seq_tok, n_heads, group,
-                                        window, scale * 1.4426950408889634f, scratch, max_splits, status);
+  fg_launch_pdl(kern, grid, dim3(THREADS), smem, stream, km, vm, layer, (const __nv_bfloat16*)q, q_stride,
+                block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_heads, group, window,
+                scale * 1.4426950408889634f, scratch, max_splits, status);
   FG_CHECK_LAUNCH("fg_attention_decode_tma_bf16");
   dim3 cgrid(n_heads, n_seqs);
-  fg_mma::attention_combine_kernel<FG_HEAD_DIM><<<cgrid, 128, 0, stream>>>(
-      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, status);
+  fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(128), 0, stream,
+                (const float*)scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
+                max_splits, status);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }

@@ -546,6 +546,8 @@ attention_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __res
   constexpr int CHUNK = 128;  // splits whose weights are staged at a time
   __shared__ float w_s[CHUNK];
   __shared__ float red[4];
+  pdl_trigger();
+  pdl_wait();
   const int seq = blockIdx.y, head = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok = seq_tok[seq];

@@ -106,6 +106,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ int box_page[SPLIT / 8];  // page of each box, -1: nothing to load
 
+  // positions, slots and block tables are inputs of the step (no kernel of the step
+  // writes them), so the page look-ups and the barrier set-up run while the kernel
+  // before this one finishes; keys, values and queries are touched after the wait
+  pdl_trigger();
   const int split = blockIdx.x, g = blockIdx.y, seq = blockIdx.z;
   const int b = seq_req[seq];
   if (b < 0) return;
@@ -139,6 +143,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_wait();
 
   if (tid == 0) {
     int n_valid = 0;

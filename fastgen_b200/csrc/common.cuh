@@ -41,6 +41,36 @@ void fg_set_error(const char* fmt, ...);
     }                                                                 \
   } while (0)
 
+// ---------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through fg_launch_pdl may start
+// while the kernel before it on the stream is still running: pdl_trigger() (first
+// statement) lets the next kernel start early in turn, and pdl_wait() blocks until
+// the previous kernel has completed and its writes are visible.  Before pdl_wait() a
+// kernel may only touch what no earlier kernel of the step writes (weights, block
+// tables, positions) and must not write global memory.  Both are no-ops for a kernel
+// launched the ordinary way.  FG_NO_PDL=1 in the environment turns the attribute off.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+bool fg_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t fg_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = fg_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>

@@ -1,6 +1,7 @@
 // Error message plumbing of the C interface.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -16,3 +17,12 @@ void fg_set_error(const char* fmt, ...) {
 extern "C" const char* fg_last_error() { return g_error; }
 
 extern "C" int fg_abi_version() { return 1; }
+
+bool fg_pdl_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* v = getenv("FG_NO_PDL");
+    state = (v != nullptr && v[0] != 0 && v[0] != '0') ? 0 : 1;
+  }
+  return state == 1;
+}

@@ -116,30 +116,41 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
   const int n_chunks = (K + CHUNK - 1) / CHUNK;
   const int my_chunks = warp < n_chunks ? (n_chunks - warp + WARPS - 1) / WARPS : 0;
 
-  // issue the copies of this thread's i-th chunk into stage i % STAGES
-  auto issue = [&](int i) {
+  // issue the copies of this thread's i-th chunk into stage i % STAGES: the pieces of
+  // W, the pieces of x, or both
+  auto issue = [&](int i, bool do_w, bool do_x) {
     uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
     const int k = (warp + i * WARPS) * CHUNK;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int kk = k + h * 32;
       const bool ok = kk + c * 8 < K;  // K is a multiple of 8: a 16-byte piece is all in or all out
-      cp_async_16<false>(slot + (2 * h) * THREADS, wa + kk, ok && row_a);
-      cp_async_16<false>(slot + (2 * h + 1) * THREADS, wb + kk, ok && row_b);
+      if (do_w) {
+        cp_async_16<false>(slot + (2 * h) * THREADS, wa + kk, ok && row_a);
+        cp_async_16<false>(slot + (2 * h + 1) * THREADS, wb + kk, ok && row_b);
+      }
+      if (do_x) {
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        cp_async_16<true>(slot + (4 + nt * 2 + h) * THREADS, xr[nt] + kk, ok && tok_ok[nt]);
+        for (int nt = 0; nt < NT; ++nt)
+          cp_async_16<true>(slot + (4 + nt * 2 + h) * THREADS, xr[nt] + kk, ok && tok_ok[nt]);
       }
     }
   };
 
+  // The weights do not depend on the kernel before this one: their first stages are on
+  // their way while that kernel finishes.  x (its output) is only touched after the wait.
+  pdl_trigger();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s)
+    if (s < my_chunks) issue(s, true, false);
+  pdl_wait();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < my_chunks) issue(s);
+    if (s < my_chunks) issue(s, false, true);
     cp_async_commit();
   }
   for (int i = 0; i < my_chunks; ++i) {
-    if (i + STAGES - 1 < my_chunks) issue(i + STAGES - 1);
+    if (i + STAGES - 1 < my_chunks) issue(i + STAGES - 1, true, true);
     cp_async_commit();
     cp_async_wait<STAGES - 1>();  // this thread's copies of chunk i have landed; only it reads them
     const uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
@@ -237,8 +248,8 @@ int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
     FG_CHECK_ARG(e == cudaSuccess, "fg_gemm_skinny: shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  kern<<<(N + ROWS - 1) / ROWS, THREADS, smem, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w,
-                                                         ldw, (TO*)y, ldy, M, N, K, qkv);
+  fg_launch_pdl(kern, dim3((N + ROWS - 1) / ROWS), dim3(THREADS), smem, stream, (const __nv_bfloat16*)x, ldx,
+                (const __nv_bfloat16*)w, ldw, (TO*)y, ldy, M, N, K, qkv);
   return 0;
 }
 

@@ -81,6 +81,8 @@ __global__ void __launch_bounds__(VEC_THREADS)
 rmsnorm_vec_kernel(TH* __restrict__ h, const TD* __restrict__ delta, const void* __restrict__ w, int w_dtype,
                    TO* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const size_t base = (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * dim;
   const size_t obase = (size_t)blockIdx.x * dim;
   const bool store_h = delta != nullptr && rows == nullptr;
@@ -121,10 +123,10 @@ template <typename TH, typename TD, typename TO>
 static void launch_vec(int items, int n_rows, cudaStream_t stream, TH* h, const TD* delta, const void* w,
                        int w_dtype, TO* out, const int* rows, int dim, float eps) {
   switch (items) {
-    case 1: rmsnorm_vec_kernel<TH, TD, TO, 1><<<n_rows, VEC_THREADS, 0, stream>>>(h, delta, w, w_dtype, out, rows, dim, eps); break;
-    case 2: rmsnorm_vec_kernel<TH, TD, TO, 2><<<n_rows, VEC_THREADS, 0, stream>>>(h, delta, w, w_dtype, out, rows, dim, eps); break;
-    case 4: rmsnorm_vec_kernel<TH, TD, TO, 4><<<n_rows, VEC_THREADS, 0, stream>>>(h, delta, w, w_dtype, out, rows, dim, eps); break;
-    default: rmsnorm_vec_kernel<TH, TD, TO, 8><<<n_rows, VEC_THREADS, 0, stream>>>(h, delta, w, w_dtype, out, rows, dim, eps); break;
+    case 1: fg_launch_pdl(rmsnorm_vec_kernel<TH, TD, TO, 1>, dim3(n_rows), dim3(VEC_THREADS), 0, stream, h, delta, w, w_dtype, out, rows, dim, eps); break;
+    case 2: fg_launch_pdl(rmsnorm_vec_kernel<TH, TD, TO, 2>, dim3(n_rows), dim3(VEC_THREADS), 0, stream, h, delta, w, w_dtype, out, rows, dim, eps); break;
+    case 4: fg_launch_pdl(rmsnorm_vec_kernel<TH, TD, TO, 4>, dim3(n_rows), dim3(VEC_THREADS), 0, stream, h, delta, w, w_dtype, out, rows, dim, eps); break;
+    default: fg_launch_pdl(rmsnorm_vec_kernel<TH, TD, TO, 8>, dim3(n_rows), dim3(VEC_THREADS), 0, stream, h, delta, w, w_dtype, out, rows, dim, eps); break;
   }
 }
 
