@@ -42,8 +42,10 @@ __device__ __forceinline__ void store_pair<__nv_bfloat16>(__nv_bfloat16* p, floa
   else { p[0] = __float2bfloat16_rn(v.x); p[1] = __float2bfloat16_rn(v.y); }
 }
 
-// One thread per adjacent pair: blockIdx.x is the token, blockIdx.y a slab of
-// 128 pairs out of [query pairs | key pairs | value pairs].
+// A thread owns one pair index j of one token: it computes sin and cos of the
+// token's angle for j once and walks the heads (queries, then keys, then values)
+// that its block is given: blockIdx.x is the token, blockIdx.y a slice of the
+// heads (few tokens get more slices, so that the GPU is still filled).
 template <typename T>
 __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
@@ -51,52 +53,50 @@ rope_kv_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_s
                const int* __restrict__ req, const float* __restrict__ freqs, T* __restrict__ k_pages,
                T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                int page_size, int n_pages, int n_heads, int n_kv_heads, int head_dim, int* status,
-               bool vec, int items_per_thread) {
+               bool vec, int heads_per_block) {
   const int t = blockIdx.x;
   const int r = req[t];
   if (r < 0) return;
   const int half = head_dim >> 1;
-  const int n_q = n_heads * half, n_kv = (k != nullptr) ? n_kv_heads * half : 0;
+  const int lanes = ROPE_THREADS / half > 0 ? ROPE_THREADS / half : 1;  // heads walked side by side
+  const int j = threadIdx.x % half, lane_head = threadIdx.x / half;
+  if (lane_head >= lanes) return;
   const int p = pos[t];
-  for (int it = 0; it < items_per_thread; ++it) {
-  const int item = (blockIdx.y * items_per_thread + it) * ROPE_THREADS + threadIdx.x;
-  if (item >= n_q + 2 * n_kv) return;
-  if (item < n_q) {
-    const int j = item % half;
-    T* x = q + (size_t)t * q_stride + (item / half) * head_dim + 2 * j;
-    const float2 v = load_pair<T>(x, vec);
-    float s = 0.f, c = 1.f;
-    if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
-    store_pair<T>(x, make_float2(v.x * c - v.y * s, v.y * c + v.x * s), vec);
-    continue;
-  }
-  const bool is_v = item >= n_q + n_kv;
-  const int kv_item = item - n_q - (is_v ? n_kv : 0);
-  const int g = kv_item / half, j = kv_item - g * half;
-  const int logical = p / page_size;
-  const int page = (logical < table_width) ? block_table[(size_t)r * table_width + logical] : -1;
-  if (page < 0 || page >= n_pages) {
-    if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
-    return;
-  }
-  const size_t dst = (((size_t)page * n_kv_heads + g) * page_size + (p - logical * page_size)) * head_dim + 2 * j;
-  if (is_v) {
-    const T* x = v + (size_t)t * v_stride + g * head_dim + 2 * j;
-    if (vec) {
-      // a plain copy: move the pair's bits
-      if (sizeof(T) == 2) *reinterpret_cast<uint32_t*>(v_pages + dst) = *reinterpret_cast<const uint32_t*>(x);
-      else *reinterpret_cast<uint2*>(v_pages + dst) = *reinterpret_cast<const uint2*>(x);
-    } else {
-      v_pages[dst] = x[0];
-      v_pages[dst + 1] = x[1];
+  const int n_kv = (k != nullptr) ? n_kv_heads : 0;
+  const int total = n_heads + 2 * n_kv;  // heads in the order q..., k..., v...
+  const int h_end = min(total, (int)(blockIdx.y + 1) * heads_per_block);
+  float s = 0.f, c = 1.f;
+  if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
+  size_t slot = 0;
+  bool have_slot = false;
+  for (int h = blockIdx.y * heads_per_block + lane_head; h < h_end; h += lanes) {
+    if (h < n_heads) {
+      T* x = q + (size_t)t * q_stride + h * head_dim + 2 * j;
+      const float2 val = load_pair<T>(x, vec);
+      store_pair<T>(x, make_float2(val.x * c - val.y * s, val.y * c + val.x * s), vec);
+      continue;
     }
-  } else {
-    const T* x = k + (size_t)t * k_stride + g * head_dim + 2 * j;
-    const float2 kv = load_pair<T>(x, vec);
-    float s = 0.f, c = 1.f;
-    if (freqs != nullptr) sincosf((float)p * freqs[j], &s, &c);
-    store_pair<T>(k_pages + dst, make_float2(kv.x * c - kv.y * s, kv.y * c + kv.x * s), vec);
-  }
+    if (!have_slot) {
+      const int logical = p / page_size;
+      const int page = (logical < table_width) ? block_table[(size_t)r * table_width + logical] : -1;
+      if (page < 0 || page >= n_pages) {
+        if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+        return;
+      }
+      slot = (size_t)page * n_kv_heads * page_size + (p - logical * page_size);
+      have_slot = true;
+    }
+    const bool is_v = h >= n_heads + n_kv;
+    const int g = h - n_heads - (is_v ? n_kv : 0);
+    const size_t dst = (slot + (size_t)g * page_size) * head_dim + 2 * j;
+    if (is_v) {
+      const T* x = v + (size_t)t * v_stride + g * head_dim + 2 * j;
+      store_pair<T>(v_pages + dst, load_pair<T>(x, vec), vec);
+    } else {
+      const T* x = k + (size_t)t * k_stride + g * head_dim + 2 * j;
+      const float2 val = load_pair<T>(x, vec);
+      store_pair<T>(k_pages + dst, make_float2(val.x * c - val.y * s, val.y * c + val.x * s), vec);
+    }
   }
 }
 
@@ -114,12 +114,13 @@ extern "C" int fg_rope_kv_write(void* q, int q_stride, const void* k, int k_stri
   FG_CHECK_ARG((k == nullptr) == (v == nullptr), "fg_rope_kv_write: k and v must both be given or both null");
   FG_CHECK_ARG(k == nullptr || (k_pages && v_pages && block_table && page_size > 0),
                "fg_rope_kv_write: cache arguments missing");
-  const int items = (n_heads + (k ? 2 * n_kv_heads : 0)) * head_dim / 2;
-  // few tokens: one pair a thread, many small blocks; many tokens: several pairs a
-  // thread, so that the number of blocks stays in the low thousands
-  int ipt = 1;
-  while (ipt < 16 && (long long)n_tokens * ((items + ROPE_THREADS * ipt - 1) / (ROPE_THREADS * ipt)) > 4096) ipt *= 2;
-  const dim3 grid(n_tokens, (items + ROPE_THREADS * ipt - 1) / (ROPE_THREADS * ipt));
+  FG_CHECK_ARG(head_dim / 2 <= ROPE_THREADS, "fg_rope_kv_write: head size %d is too large", head_dim);
+  const int total_heads = n_heads + (k ? 2 * n_kv_heads : 0);
+  // many tokens: one block a token; few tokens: slices of heads, so that there are enough blocks
+  int slices = n_tokens >= 1024 ? 1 : (n_tokens >= 128 ? 4 : 16);
+  if (slices > total_heads) slices = total_heads;
+  const int ipt = (total_heads + slices - 1) / slices;  // heads per block
+  const dim3 grid(n_tokens, (total_heads + ipt - 1) / ipt);
   const int threads = ROPE_THREADS;
   FG_CHECK_ARG(grid.y <= 65535, "fg_rope_kv_write: too many heads");
   const size_t pair = dtype == FG_F32 ? 8 : 4;
