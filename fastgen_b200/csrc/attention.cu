@@ -252,6 +252,55 @@ extern "C" int fg_attention_prefill_tma_bf16(const void* q, int q_stride, void* 
   FG_CHECK_LAUNCH("fg_attention_prefill_tma_bf16");
   return 0;
 }
+
+#if FG_HEAD_DIM == 64 || FG_HEAD_DIM == 128
+#include "attention_tcgen05.cuh"
+
+extern "C" int fg_attention_prefill_tc5_supported() { return 1; }
+
+// Prompt portions on tcgen05 / TMEM.  Same arguments and tiling (128 rows a block) as
+// fg_attention_prefill_tma_bf16; the tensor maps must have boxes of min(page, 64) rows.
+extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                             const void* k_map, const void* v_map, int layer,
+                                             const int* block_table, int table_width, int page_size,
+                                             int n_pages, const int* pos, const int* tile_req,
+                                             const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                                             int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                             int* status, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tc5_bf16: library built for head size %d, got %d",
+               FG_HEAD_DIM, head_dim);
+  FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
+               "fg_attention_prefill_tc5_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
+               "fg_attention_prefill_tc5_bf16: pages of %d slots are not supported", page_size);
+  FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0,
+               "fg_attention_prefill_tc5_bf16: queries and outputs must be 16-byte aligned with strides multiple of 8");
+  const int group = n_heads / n_kv_heads;
+  const int hpb = group < fg_tc5::ROWS ? group : fg_tc5::ROWS;
+  CUtensorMap km, vm;
+  memcpy(&km, k_map, sizeof(CUtensorMap));
+  memcpy(&vm, v_map, sizeof(CUtensorMap));
+  constexpr size_t smem = fg_tc5::smem_bytes<FG_HEAD_DIM>();
+  auto kern = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_tc5_bf16: shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
+  kern<<<grid, fg_tc5::THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
+                                        out_stride, block_table, table_width, page_size, n_pages, pos, tile_req,
+                                        tile_tok0, tile_ntok, n_tiles, group, hpb, window,
+                                        scale * 1.4426950408889634f, status);
+  FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
+  return 0;
+}
+#else
+extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
+#endif
 #else
 extern "C" int fg_attention_decode_tma_supported() { return 0; }
+extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
 #endif

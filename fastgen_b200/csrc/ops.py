@@ -10,6 +10,7 @@ here falls back to the CPU or to eager PyTorch.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -60,6 +61,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P,
                                  ctypes.c_longlong, _I, _P, _P],
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
+                                      _I, _F, _P, _P],
+    "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, _P, _P],
@@ -168,6 +171,7 @@ class Ops:
         self.lib = core()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch = {}
+        self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
         # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -376,7 +380,11 @@ class Ops:
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
         tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, rows), 2)
         if tiles.n and use_tma:
-            _check(lib, lib.fg_attention_prefill_tma_bf16(
+            # head sizes 64 and 128: tcgen05.mma with S and O in tensor memory; other
+            # multiples of 64: mma.sync on the same TMA tiles (FG_NO_TCGEN05=1 forces that)
+            fn = (lib.fg_attention_prefill_tc5_bf16 if head_dim in (64, 128) and self.use_tcgen05
+                  else lib.fg_attention_prefill_tma_bf16)
+            _check(lib, fn(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[2].ptr,
                 memory.tensor_maps[3].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
                 page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),

@@ -335,9 +335,15 @@ def test_attention(ops32, ops16, case):
     seqs, hq, hkv, hd, page, window = CASES[case]
     out, ref = _attention_case(ops32, seqs, hq, hkv, hd, page, window, case)
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5), float((out - ref).abs().max())
-    for use_tma in (True, False):  # tiled TMA loads where the shape allows, else (and also) cp.async
-        out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, case, use_tma=use_tma)
-        assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), float((out - ref).abs().max())
+    # tiled TMA loads where the shape allows (prompts on tcgen05 for head sizes 64 and 128,
+    # then on mma.sync), else (and also) cp.async
+    for use_tma, tc5 in ((True, True), (True, False), (False, False)):
+        ops16.use_tcgen05 = tc5
+        try:
+            out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, case, use_tma=use_tma)
+        finally:
+            ops16.use_tcgen05 = True
+        assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), (use_tma, tc5, float((out - ref).abs().max()))
 
 
 @pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
