@@ -6,13 +6,14 @@
 // A block owns 128 query rows (consecutive tokens of one request x the query
 // heads of one key/value head) and walks the request's keys in tiles of 64:
 //
-//   thread 0:  TMA(K_t+1, V_t+1);  S_{t+1} = Q K_{t+1}^T   (tcgen05.mma, M128 N64 K16 x HD/16)
-//   all 128:   S_t from TMEM (one row a thread: no shuffles for max and sum),
-//              p = 2^((s - m) c),  P_t -> shared memory (bf16, operand layout)
-//   thread 0:  O += P_t V_t                                 (tcgen05.mma, M128 N=HD K16 x 4)
+//   control warp:   TMA(K_t+1, V_t+1);  S_{t+1} = Q K_{t+1}^T  (tcgen05.mma, M128 N64 K16 x HD/16)
+//   4 softmax warps: S_t from TMEM (one row a thread: no shuffles for max and sum),
+//                    p = 2^((s - m) c),  P_t (bf16) back into TMEM over S_t's columns
+//   control warp:   O += P_t V_t      (tcgen05.mma with A from TMEM, M128 N=HD K16 x 4)
 //
-// so the tensor core computes S_{t+1} and O_t while the threads are busy with the
-// exponentials.  The running maximum is only raised when a row's maximum grew by
+// The warps only meet at mbarriers (scores ready, probabilities ready, output
+// done), so the tensor core computes S_{t+1} and O_t while the softmax warps are
+// busy with the exponentials, and two blocks share an SM.  The running maximum is only raised when a row's maximum grew by
 // more than 2^8 (the accumulated O is then rescaled in TMEM), which is exact:
 // m is just the reference point of the exponent.
 //
@@ -34,7 +35,8 @@ using fg_tma::tma_load_5d;
 
 constexpr int ROWS = 128;     // query rows a block
 constexpr int KEYS = 64;      // key positions a tile
-constexpr int THREADS = 128;
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int THREADS = 160;  // 4 softmax warps + 1 control warp
 constexpr int KV_HALF = KEYS * 128;   // bytes of one 64-element half of a K or V tile
 constexpr int Q_HALF = ROWS * 128;    // ... of the Q tile
 constexpr float RESCALE_THRESHOLD = 8.f;  // in units of log2
@@ -62,6 +64,15 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]: A is 128 lanes x 8 columns of packed bf16 pairs
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // the mbarrier gets one arrival when every tcgen05 operation issued so far by this thread is done
@@ -105,6 +116,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st32_raw(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31,%32};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
 // `lbo_bytes`: for a K-major operand 16 (unused by the hardware for swizzled layouts);
 // for an MN-major operand the distance between 64-element groups along M/N.
@@ -121,10 +145,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 
 template <int HD>
 constexpr size_t smem_bytes() {
-  // Q, two stages of K and V, P; plus alignment slack
-  return (size_t)ROWS * HD * 2 + 2 * 2 * (size_t)KEYS * HD * 2 + (size_t)ROWS * KEYS * 2 + 1024;
+  // Q and two stages of K and V; plus alignment slack
+  return (size_t)ROWS * HD * 2 + 2 * 2 * (size_t)KEYS * HD * 2 + 1024;
 }
-constexpr int TMEM_COLS = 256;  // S0, S1 (64 columns each) + O (HD <= 128), a power of two
+constexpr int TMEM_COLS = 256;  // S0, S1 (64 columns each; P overwrites its S) + O (HD <= 128)
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
@@ -146,11 +170,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   unsigned char* Qs = smem;                         // [HALVES][128 rows][128 B]
   unsigned char* Ks = Qs + HALVES * Q_HALF;         // [2][HALVES][64 rows][128 B]
   unsigned char* Vs = Ks + 2 * STAGE_BYTES;
-  unsigned char* Ps = Vs + 2 * STAGE_BYTES;         // [128 rows][128 B]
-  __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], o_done;
+  // full_k/full_v: a tile's keys/values have landed; s_done: its scores are in TMEM;
+  // p_ready: all 128 softmax threads stored its probabilities; o_done: its P V is done
+  __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int row_pos[ROWS];
-  constexpr int PAGE_STAGE = 512;
+  __shared__ int first_pos_s;
+  constexpr int PAGE_STAGE = 256;
   __shared__ int box_pages[PAGE_STAGE];
 
   const int tile = n_tiles_total - 1 - blockIdx.x;  // heavy tiles first
@@ -159,16 +184,19 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (b < 0) return;
+  const bool softmax_thread = tid < SOFTMAX_THREADS;
 
   auto row_token = [&](int r) { return r / heads_per_block; };
   auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
   auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
 
-  const bool my_valid = row_valid(tid);
-  const int my_pos = my_valid ? pos[tok0 + row_token(tid)] : -1;
-  row_pos[tid] = my_pos;
-  // queries -> shared memory in the K-major operand layout (16-byte pieces, swizzled)
-  {
+  bool my_valid = false;
+  int my_pos = -1;
+  if (softmax_thread) {
+    my_valid = row_valid(tid);
+    my_pos = my_valid ? pos[tok0 + row_token(tid)] : -1;
+    if (tid == 0) first_pos_s = my_pos;
+    // queries -> shared memory in the K-major operand layout (16-byte pieces, swizzled)
     const __nv_bfloat16* src = q + (size_t)(tok0 + row_token(tid)) * q_stride + (g * group + row_head(tid)) * HD;
 #pragma unroll
     for (int c = 0; c < HD / 8; ++c) {
@@ -176,14 +204,18 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       if (my_valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
       *reinterpret_cast<uint4*>(Qs + (c / 8) * Q_HALF + fg_tma::swz(tid, c % 8)) = v;
     }
+    fence_async_smem();  // written by ordinary stores, read by the tensor core
   }
-  if (tid == 0) {
+  if (tid == SOFTMAX_THREADS) {
     mbar_init(&full_k[0], 1);
     mbar_init(&full_k[1], 1);
     mbar_init(&full_v[0], 1);
     mbar_init(&full_v[1], 1);
     mbar_init(&s_done[0], 1);
     mbar_init(&s_done[1], 1);
+    // two of them: a softmax warp may be one tile ahead of another
+    mbar_init(&p_ready[0], SOFTMAX_THREADS);
+    mbar_init(&p_ready[1], SOFTMAX_THREADS);
     mbar_init(&o_done, 1);
     mbar_fence_init();
   }
@@ -191,240 +223,232 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     tmem_alloc(&tmem_base_s, TMEM_COLS);
     tmem_relinquish();
   }
-  fence_async_smem();  // the queries were written by ordinary stores, the tensor core reads them
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
 
-  const int min_pos = row_pos[0];
+  const int min_pos = first_pos_s;  // tokens of a tile are consecutive positions
   const int max_pos = min_pos + ntok - 1;
   const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
   const int k_lo = k_begin / KEYS * KEYS;
   const int k_end = max_pos + 1;
   const int n_tiles = (k_end - k_lo + KEYS - 1) / KEYS;
-  const int* table_row = block_table + (size_t)b * table_width;
-  const int box_rows = min(page_size, KEYS);
-  const int n_boxes = KEYS / box_rows;
-  const int tiles_per_fill = PAGE_STAGE / n_boxes;
 
-  auto fill_pages = [&](int t_first) {
-    const int n = min(tiles_per_fill, n_tiles - t_first) * n_boxes;
-    for (int x = tid; x < n; x += THREADS) {
-      const int j0 = k_lo + t_first * KEYS + x * box_rows;
-      int page = -1;
-      if (j0 < k_end && j0 + box_rows > k_begin) {
-        const int logical = j0 / page_size;
-        page = logical < table_width ? table_row[logical] : -1;
-        if (page < 0 || page >= n_pages) {
-          if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
-          page = -1;
+  if (!softmax_thread) {
+    // =============================== control warp ===============================
+    const int* table_row = block_table + (size_t)b * table_width;
+    const int box_rows = min(page_size, KEYS);
+    const int n_boxes = KEYS / box_rows;
+    const int tiles_per_fill = PAGE_STAGE / n_boxes;
+    // page ids of a stretch of key tiles, looked up by the warp's 32 lanes
+    auto fill_pages = [&](int t_first) {
+      const int n = min(tiles_per_fill, n_tiles - t_first) * n_boxes;
+      for (int x = lane; x < n; x += 32) {
+        const int j0 = k_lo + t_first * KEYS + x * box_rows;
+        int page = -1;
+        if (j0 < k_end && j0 + box_rows > k_begin) {
+          const int logical = j0 / page_size;
+          page = logical < table_width ? table_row[logical] : -1;
+          if (page < 0 || page >= n_pages) {
+            if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+            page = -1;
+          }
         }
+        box_pages[x] = page;
       }
-      box_pages[x] = page;
-    }
-  };
-  auto box_page = [&](int t, int i) { return box_pages[(t % tiles_per_fill) * n_boxes + i]; };
-  // thread 0: bring tile t's keys (or values) into stage t & 1
-  auto issue_load = [&](int t, bool values) {
-    const int stage = t & 1;
-    int n_valid = 0;
-    for (int i = 0; i < n_boxes; ++i) n_valid += box_page(t, i) >= 0;
-    uint64_t* bar = values ? &full_v[stage] : &full_k[stage];
-    mbar_arrive_expect(bar, n_valid * box_rows * HD * 2);
-    const int slot = page_size > KEYS ? (k_lo + t * KEYS) % page_size : 0;
-    unsigned char* base = (values ? Vs : Ks) + stage * STAGE_BYTES;
-    for (int i = 0; i < n_boxes; ++i) {
-      const int page = box_page(t, i);
-      if (page < 0) continue;
-#pragma unroll
-      for (int h = 0; h < HALVES; ++h)
-        tma_load_5d(base + h * KV_HALF + i * box_rows * 128, values ? &v_map : &k_map, h * 64, slot, g, page, layer,
-                    bar);
-    }
-  };
-  // all threads: boxes of tile t that are not loaded must hold zeros
-  auto zero_missing = [&](int t) -> bool {
-    bool any = false;
-    for (int i = 0; i < n_boxes; ++i) {
-      if (box_page(t, i) >= 0) continue;
-      any = true;
-      const uint4 z = make_uint4(0, 0, 0, 0);
-      for (int h = 0; h < HALVES; ++h)
-        for (int c = tid; c < box_rows * 8; c += THREADS) {
-          *reinterpret_cast<uint4*>(Ks + (t & 1) * STAGE_BYTES + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
-          *reinterpret_cast<uint4*>(Vs + (t & 1) * STAGE_BYTES + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
+      __syncwarp();
+    };
+    auto box_page = [&](int t, int i) { return box_pages[(t % tiles_per_fill) * n_boxes + i]; };
+    // bring tile t's keys (or values) into stage t & 1; boxes that hold no position of
+    // the request are zero-filled instead (a masked probability times garbage could be NaN)
+    auto load_tile = [&](int t, bool values) {
+      const int stage = t & 1;
+      unsigned char* base = (values ? Vs : Ks) + stage * STAGE_BYTES;
+      uint64_t* bar = values ? &full_v[stage] : &full_k[stage];
+      int n_valid = 0;
+      bool zeroed = false;
+      for (int i = 0; i < n_boxes; ++i) {
+        if (box_page(t, i) >= 0) {
+          ++n_valid;
+          continue;
         }
-    }
-    return any;
-  };
-  // thread 0: S[t & 1] = Q K_t^T
-  auto issue_s = [&](int t) {
-    const int stage = t & 1;
-    mbar_wait(&full_k[stage], (t >> 1) & 1, status);
-    tc_fence_after();
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-      const uint64_t a = smem_desc(Qs + (kk / 4) * Q_HALF + (kk % 4) * 32, 16);
-      const uint64_t bd = smem_desc(Ks + stage * STAGE_BYTES + (kk / 4) * KV_HALF + (kk % 4) * 32, 16);
-      umma_f16(tmem + COL_S0 + stage * KEYS, a, bd, IDESC_S, kk > 0 ? 1u : 0u);
-    }
-    umma_commit(&s_done[stage]);
-  };
-
-  fill_pages(0);
-  __syncthreads();
-  if (zero_missing(0)) {
-    fence_async_smem();
-    __syncthreads();
-  }
-  if (tid == 0) {
-    issue_load(0, false);
-    issue_load(0, true);
-    issue_s(0);
-  }
-
-  float m_ref = -INFINITY, l_run = 0.f;
-  const float c = scale_log2;
-  // whether every row of this warp is a query, and the warp's extreme positions (for the mask shortcut)
-  const bool warp_full = __all_sync(0xffffffffu, my_valid);
-  int warp_max = my_pos, warp_min = my_valid ? my_pos : 0x7fffffff;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, o));
-    warp_min = min(warp_min, __shfl_xor_sync(0xffffffffu, warp_min, o));
-  }
-
-  for (int t = 0; t < n_tiles; ++t) {
-    const int stage = t & 1;
-    // ---- the next tile's keys start now: their stage was last read by S_{t-1}, long done.
-    //      (Its values and its scores follow below, once O_{t-1} has released that stage.)
-    if (t + 1 < n_tiles) {
-      if ((t + 1) % tiles_per_fill == 0) {
-        __syncthreads();
-        fill_pages(t + 1);
-        __syncthreads();
+        zeroed = true;
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int h = 0; h < HALVES; ++h)
+          for (int c = lane; c < box_rows * 8; c += 32)
+            *reinterpret_cast<uint4*>(base + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
       }
-      if (tid == 0) issue_load(t + 1, false);
-    }
-    // ---- this tile's scores ----
-    mbar_wait(&s_done[stage], (t >> 1) & 1, status);
-    tc_fence_after();
-    const int k0 = k_lo + t * KEYS;
-    float s[KEYS];
-    {
-      float part[32];
-      tmem_ld32(tmem + my_lane + COL_S0 + stage * KEYS, part);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s[i] = part[i];
-      tmem_ld32(tmem + my_lane + COL_S0 + stage * KEYS + 32, part);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
-    }
-    const bool need_mask = !warp_full || k0 + KEYS - 1 > warp_min || (window > 0 && k0 <= warp_max - window);
-    if (need_mask) {
-#pragma unroll
-      for (int i = 0; i < KEYS; ++i) {
-        const int j = k0 + i;
-        const bool vis = my_pos >= 0 && j <= my_pos && (window <= 0 || j > my_pos - window);
-        if (!vis) s[i] = -INFINITY;
-      }
-    }
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < KEYS; ++i) mx = fmaxf(mx, s[i]);
-    // raise the reference maximum only when it pays (or when there is none yet)
-    float alpha = 1.f;
-    bool raise = false;
-    if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * c > RESCALE_THRESHOLD)) {
-      raise = true;
-      alpha = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * c);
-      m_ref = mx;
-    }
-    float sum = 0.f;
-    uint32_t packed[KEYS / 2];
-    if (m_ref == -INFINITY) {
-#pragma unroll
-      for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
-    } else {
-      const float mc = m_ref * c;
-#pragma unroll
-      for (int i = 0; i < KEYS; i += 2) {
-        const float p0 = exp2f(fmaf(s[i], c, -mc)), p1 = exp2f(fmaf(s[i + 1], c, -mc));
-        sum += p0 + p1;
-        packed[i / 2] = pack_bf16(p0, p1);
-      }
-    }
-    l_run = l_run * alpha + sum;
-
-    // ---- the previous tile's O must be complete before P, the V stage or O itself change ----
-    if (t > 0) {
-      mbar_wait(&o_done, (t - 1) & 1, status);
-      tc_fence_after();
-    }
-    // the next tile's values go into the stage that O_{t-1} just released; then its scores
-    if (t + 1 < n_tiles) {
-      if (zero_missing(t + 1)) {
+      if (zeroed) {
         fence_async_smem();
-        __syncthreads();
+        __syncwarp();
       }
-      if (tid == 0) {
-        issue_load(t + 1, true);
+      if (lane == 0) {
+        mbar_arrive_expect(bar, n_valid * box_rows * HD * 2);
+        const int slot = page_size > KEYS ? (k_lo + t * KEYS) % page_size : 0;
+        for (int i = 0; i < n_boxes; ++i) {
+          const int page = box_page(t, i);
+          if (page < 0) continue;
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_5d(base + h * KV_HALF + i * box_rows * 128, values ? &v_map : &k_map, h * 64, slot, g, page,
+                        layer, bar);
+        }
+      }
+      __syncwarp();
+    };
+    // S[t & 1] = Q K_t^T
+    auto issue_s = [&](int t) {
+      const int stage = t & 1;
+      mbar_wait(&full_k[stage], (t >> 1) & 1, status);
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t a = smem_desc(Qs + (kk / 4) * Q_HALF + (kk % 4) * 32, 16);
+          const uint64_t bd = smem_desc(Ks + stage * STAGE_BYTES + (kk / 4) * KV_HALF + (kk % 4) * 32, 16);
+          umma_f16(tmem + COL_S0 + stage * KEYS, a, bd, IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_done[stage]);
+      }
+      __syncwarp();
+    };
+
+    fill_pages(0);
+    load_tile(0, false);
+    load_tile(0, true);
+    issue_s(0);
+    for (int t = 0; t < n_tiles; ++t) {
+      const int stage = t & 1;
+      if (t + 1 < n_tiles) {
+        if ((t + 1) % tiles_per_fill == 0) fill_pages(t + 1);
+        // the keys' stage was last read by S_{t-1}, which finished before S_t did
+        load_tile(t + 1, false);
+      }
+      if (t > 0) {
+        // O_{t-1} done: its values' stage and the columns of S_{t-1} / P_{t-1} are free
+        mbar_wait(&o_done, (t - 1) & 1, status);
+        tc_fence_after();
+      }
+      if (t + 1 < n_tiles) {
+        load_tile(t + 1, true);
         issue_s(t + 1);
       }
-    }
-    // rescale O where a row's reference maximum was raised (warp-uniform decision)
-    if (t > 0 && __any_sync(0xffffffffu, raise)) {
-#pragma unroll
-      for (int cc = 0; cc < HD / 32; ++cc) {
-        float part[32];
-        tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) part[i] *= alpha;
-        tmem_st32(tmem + my_lane + COL_O + cc * 32, part);
-      }
-    }
-    // P -> shared memory, K-major operand layout: row tid, 8 pieces of 8 keys
-#pragma unroll
-    for (int ch = 0; ch < KEYS / 8; ++ch)
-      *reinterpret_cast<uint4*>(Ps + fg_tma::swz(tid, ch)) =
-          make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    // ---- O += P V_t ----
-    if (tid == 0) {
-      tc_fence_after();
+      // all softmax threads have stored P_t (and rescaled O where needed)
+      mbar_wait(&p_ready[stage], (t >> 1) & 1, status);
       mbar_wait(&full_v[stage], (t >> 1) & 1, status);
+      tc_fence_after();
+      if (lane == 0) {
 #pragma unroll
-      for (int j = 0; j < KEYS / 16; ++j) {
-        const uint64_t a = smem_desc(Ps + j * 32, 16);
-        const uint64_t bd = smem_desc(Vs + stage * STAGE_BYTES + j * 16 * 128, KV_HALF);
-        umma_f16(tmem + COL_O, a, bd, IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
+        for (int j = 0; j < KEYS / 16; ++j) {
+          const uint64_t bd = smem_desc(Vs + stage * STAGE_BYTES + j * 16 * 128, KV_HALF);
+          umma_f16_ts(tmem + COL_O, tmem + COL_S0 + stage * KEYS + j * 8, bd, IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_done);
       }
-      umma_commit(&o_done);
+      __syncwarp();
     }
-  }
-
-  // ---- O / l -> out ----
-  mbar_wait(&o_done, (n_tiles - 1) & 1, status);
-  tc_fence_after();
-  const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-  __nv_bfloat16* dst = out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;
+  } else {
+    // =============================== softmax warps ===============================
+    const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
+    float m_ref = -INFINITY, l_run = 0.f;
+    const float c = scale_log2;
+    const bool warp_full = __all_sync(0xffffffffu, my_valid);
+    int warp_max = my_pos, warp_min = my_valid ? my_pos : 0x7fffffff;
 #pragma unroll
-  for (int cc = 0; cc < HD / 32; ++cc) {
-    float part[32];
-    tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
-    if (my_valid) {
+    for (int o = 16; o > 0; o >>= 1) {
+      warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, o));
+      warp_min = min(warp_min, __shfl_xor_sync(0xffffffffu, warp_min, o));
+    }
+    for (int t = 0; t < n_tiles; ++t) {
+      const int stage = t & 1;
+      const uint32_t s_addr = tmem + my_lane + COL_S0 + stage * KEYS;
+      mbar_wait(&s_done[stage], (t >> 1) & 1, status);
+      tc_fence_after();
+      const int k0 = k_lo + t * KEYS;
+      float s[KEYS];
+      {
+        float part[32];
+        tmem_ld32(s_addr, part);
 #pragma unroll
-      for (int i = 0; i < 32; i += 8) {
-        uint4 v;
-        v.x = pack_bf16(part[i] * inv, part[i + 1] * inv);
-        v.y = pack_bf16(part[i + 2] * inv, part[i + 3] * inv);
-        v.z = pack_bf16(part[i + 4] * inv, part[i + 5] * inv);
-        v.w = pack_bf16(part[i + 6] * inv, part[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + cc * 32 + i) = v;
+        for (int i = 0; i < 32; ++i) s[i] = part[i];
+        tmem_ld32(s_addr + 32, part);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
+      }
+      const bool need_mask = !warp_full || k0 + KEYS - 1 > warp_min || (window > 0 && k0 <= warp_max - window);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < KEYS; ++i) {
+          const int j = k0 + i;
+          const bool vis = my_pos >= 0 && j <= my_pos && (window <= 0 || j > my_pos - window);
+          if (!vis) s[i] = -INFINITY;
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < KEYS; ++i) mx = fmaxf(mx, s[i]);
+      // raise the reference maximum only when it pays (or when there is none yet)
+      float alpha = 1.f;
+      bool raise = false;
+      if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * c > RESCALE_THRESHOLD)) {
+        raise = true;
+        alpha = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * c);
+        m_ref = mx;
+      }
+      float sum = 0.f;
+      uint32_t packed[KEYS / 2];
+      if (m_ref == -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
+      } else {
+        const float mc = m_ref * c;
+#pragma unroll
+        for (int i = 0; i < KEYS; i += 2) {
+          const float p0 = exp2f(fmaf(s[i], c, -mc)), p1 = exp2f(fmaf(s[i + 1], c, -mc));
+          sum += p0 + p1;
+          packed[i / 2] = pack_bf16(p0, p1);
+        }
+      }
+      l_run = l_run * alpha + sum;
+      // P_t over the first 32 columns of S_t (this thread has read all of its row)
+      tmem_st32_raw(s_addr, packed);
+      // rescale O where a row's reference maximum was raised (warp-uniform decision);
+      // O_{t-1} must be complete first
+      if (t > 0 && __any_sync(0xffffffffu, raise)) {
+        mbar_wait(&o_done, (t - 1) & 1, status);
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < HD / 32; ++cc) {
+          float part[32];
+          tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) part[i] *= alpha;
+          tmem_st32(tmem + my_lane + COL_O + cc * 32, part);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&p_ready[stage]);
+    }
+    // ---- O / l -> out ----
+    mbar_wait(&o_done, (n_tiles - 1) & 1, status);
+    tc_fence_after();
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* dst = out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;
+#pragma unroll
+    for (int cc = 0; cc < HD / 32; ++cc) {
+      float part[32];
+      tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
+      if (my_valid) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = pack_bf16(part[i] * inv, part[i + 1] * inv);
+          v.y = pack_bf16(part[i + 2] * inv, part[i + 3] * inv);
+          v.z = pack_bf16(part[i + 4] * inv, part[i + 5] * inv);
+          v.w = pack_bf16(part[i + 6] * inv, part[i + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + cc * 32 + i) = v;
+        }
       }
     }
   }
