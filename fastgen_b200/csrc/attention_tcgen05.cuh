@@ -413,10 +413,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       l_run = l_run * alpha + sum;
       // P_t over the first 32 columns of S_t (this thread has read all of its row)
       tmem_st32_raw(s_addr, packed);
-      // rescale O where a row's reference maximum was raised (warp-uniform decision);
-      // O_{t-1} must be complete first
+      // Every completion of o_done is awaited in turn, needed or not: a parity wait can
+      // only tell "this phase is over" from "not yet" if the waiter never falls two
+      // phases behind.  O_{t-1} is complete after it; O is then rescaled where a row's
+      // reference maximum was raised (warp-uniform decision).
+      if (t > 0) mbar_wait(&o_done, (t - 1) & 1, status);
       if (t > 0 && __any_sync(0xffffffffu, raise)) {
-        mbar_wait(&o_done, (t - 1) & 1, status);
         tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < HD / 32; ++cc) {
