@@ -257,7 +257,7 @@ def run_ours(args) -> dict:
         e2e = dict(value=round(e2e_tokens / e2e_s, 1), unit="tokens/s",
                    h2d_bytes_per_step=int(sum(s["h2d_bytes"] for s in tail) / len(tail)),
                    d2h_bytes_per_step=int(sum(s["d2h_bytes"] for s in tail) / len(tail)),
-                   steps=len(tail), generated=n_out)
+                   steps=len(tail), generated=n_out, host_sync_every_steps=fg.gen_args.sync_freq)
         fg.destroy()
 
     return {

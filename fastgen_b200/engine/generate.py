@@ -199,6 +199,39 @@ class Fastgen:
         finally:
             self.generating = False
 
+    def _decode_run(self, n_steps: int):
+        """``n_steps`` decode steps of all running requests; the sampled tokens feed the
+        next step on the device and come to the host once, at the end."""
+        sched, engine = self.scheduler, self.engine
+        reqs = list(sched.running)
+        handles = [engine.cache.get(id(r)) for r in reqs]
+        slots = [h.slot for h in handles]
+        temps = [r.temperature for r in reqs]
+        keys = [r.key for r in reqs]
+        t_start = time.perf_counter()
+        engine.cache.flush_tables()
+        tokens = [r.generated[-1] if r.generated else r.prompt[-1] for r in reqs]
+        outs, lps = [], []
+        for k in range(n_steps):
+            logits = engine.graphs.run(tokens, [h.length + k for h in handles], slots)
+            out, lp = self.sampler.sample(logits, temps, keys, [len(r) + k for r in reqs])
+            outs.append(out)
+            lps.append(lp)
+            tokens = out  # stays on the device
+        sampled = torch.stack(outs).tolist()  # the run's one device-to-host read
+        logprobs = torch.stack(lps).tolist() if lps[0] is not None else None
+        self.steps += n_steps
+        t_end = time.perf_counter()
+        for k in range(n_steps):
+            self.step_log.append(dict(
+                t_start=t_start + (t_end - t_start) * k / n_steps,
+                t_end=t_start + (t_end - t_start) * (k + 1) / n_steps,
+                decode_tokens=len(reqs), prompt_tokens=0,
+                h2d_bytes=engine.graphs.last_h2d_bytes, d2h_bytes=4 * len(reqs),
+            ))
+        for req in sched.commit_decode_run(reqs, sampled, logprobs):
+            yield self._packet(req)
+
     @torch.inference_mode()
     def _generate(self, q):
         sched = self.scheduler
@@ -207,6 +240,13 @@ class Fastgen:
             eoq = self._pull(q, eoq)
             for req in sched.take_finished():
                 yield self._packet(req)
+            # several decode steps without a host round trip, when nothing else is to be decided
+            n_run = 1
+            if self.engine.graphs is not None and q.empty():
+                n_run = sched.plan_decode_run(self.gen_args.sync_freq)
+            if n_run > 1:
+                yield from self._decode_run(n_run)
+                continue
             plan = sched.plan()
             if not plan:
                 if sched.has_work():

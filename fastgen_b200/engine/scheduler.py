@@ -170,6 +170,61 @@ class Scheduler:
             budget -= n
         return entries
 
+    def plan_decode_run(self, max_steps: int) -> int:
+        """How many decode steps may run back to back without the host looking at the
+        tokens in between (the reference's ``sync_freq``, generate.py:692-699): more than
+        one only when every running request is decoding, nothing waits for admission,
+        nobody reaches its length limit inside the run and the pages for the whole run
+        can be reserved now.  Returns 1 when the ordinary one-step path should be taken."""
+        if max_steps <= 1 or not self.running or self.waiting:
+            return 1
+        n = max_steps
+        for req in self.running:
+            if len(req) - req.fed != 1:
+                return 1
+            n = min(n, req.maxlen - len(req))
+            if req.max_gen is not None:
+                n = min(n, req.max_gen - len(req.generated))
+        if n <= 1:
+            return 1
+        for req in self.running:
+            if any(need > free for need, free in zip(
+                    self.cache.pages_needed(self.cache.get(id(req)), req.fed + n), self.cache.free_pages())):
+                return 1
+        try:
+            for req in self.running:
+                self.cache.reserve(self.cache.get(id(req)), req.fed + n)
+        except OutOfPages:
+            return 1  # what was reserved stays with its request; the one-step path decides
+        return n
+
+    def commit_decode_run(self, requests: Sequence[Request], sampled: Sequence[Sequence[int]],
+                          logprobs: Optional[Sequence[Sequence[float]]] = None) -> List[Request]:
+        """Record a run of ``len(sampled)`` decode steps: ``sampled[k][i]`` is the token
+        request ``i`` drew at step ``k``.  A request's tokens are cut after its first stop
+        token (what it decoded after that is dropped, generate.py:647-662)."""
+        n = len(sampled)
+        done: List[Request] = []
+        for i, req in enumerate(requests):
+            handle = self.cache.get(id(req))
+            self.cache.advance(handle, req.fed + n)
+            req.fed += n
+            ended = False
+            for k in range(n):
+                tok = int(sampled[k][i])
+                req.generated.append(tok)
+                if logprobs is not None:
+                    req.logprobs.append(float(logprobs[k][i]))
+                if tok in self.stop_tokens or len(req) >= req.maxlen or (
+                        req.max_gen is not None and len(req.generated) >= req.max_gen):
+                    ended = True
+                    break
+            if ended:
+                self.cache.release(id(req))
+                self.running.remove(req)
+                done.append(req)
+        return done
+
     def commit(self, entries: Sequence[PlanEntry], sampled: Sequence[int],
                logprobs: Optional[Sequence[float]] = None) -> List[Request]:
         """Record a step's outcome.  ``sampled`` holds one token per entry that

@@ -148,3 +148,29 @@ def test_random_load_with_few_pages(seed):
         cap = min(r.max_gen, sched.capacity - len(prompts[r.thread_id]))
         assert r.generated == expected(prompts[r.thread_id], cap)
     assert cache.n_live == 0 and cache.free_pages() == [cache.groups[0].pool.n_pages]
+
+
+def test_decode_runs_of_several_steps():
+    """Several decode steps without looking at the tokens in between: only when every
+    request decodes, nothing waits and nobody hits a limit inside the run; tokens after a
+    stop token are dropped."""
+    sched, cache = make(n_pages=64, page=8, budget=64, stop=[50])
+    a = sched.add("a", [1, 2, 3], max_gen=20)
+    b = sched.add("b", [4, 5, 6, 7], max_gen=7)
+    assert sched.plan_decode_run(10) == 1          # prompts are not in yet
+    plan = sched.plan()
+    sched.commit(plan, [10, 20])
+    assert sched.plan_decode_run(10) == 6          # b may generate 6 more
+    assert cache.get(id(a)).length == 3 and len(cache.get(id(a)).pages[0]) >= 2  # pages for the run are held
+    done = sched.commit_decode_run([a, b], [[11, 21], [12, 22], [50, 23], [13, 24], [14, 25], [15, 26]])
+    assert a.generated == [10, 11, 12, 50] and b.generated == [20, 21, 22, 23, 24, 25, 26]
+    assert {r.thread_id for r in done} == {"a", "b"} and not sched.has_work()
+    cache.check()
+    assert cache.free_pages() == [64]
+    # a waiting request, or too few pages, mean one step at a time
+    sched, cache = make(n_pages=2, page=8, budget=64)
+    a = sched.add("a", list(range(1, 8)), max_gen=30)
+    sched.commit(sched.plan(), [9])
+    assert sched.plan_decode_run(10) == 1 or cache.free_pages() == [0]
+    c = sched.add("c", [1, 2, 3], max_gen=3)
+    assert sched.plan_decode_run(10) == 1
