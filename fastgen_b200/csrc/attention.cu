@@ -197,10 +197,33 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
     FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  dim3 grid(max_splits, n_kv_heads, n_seqs);
-  fg_launch_pdl(kern, grid, dim3(THREADS), smem, stream, km, vm, layer, (const __nv_bfloat16*)q, q_stride,
-                block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_heads, group, window,
-                scale * 1.4426950408889634f, scratch, max_splits, status);
+  // several splits for every SM: the persistent kernel (one block an SM, a producer warp
+  // a stage ahead of the consumers); fewer: one block a split, three blocks an SM
+  const long long items = (long long)max_splits * n_kv_heads * n_seqs;
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (items >= 4 * n_sms) {
+    constexpr size_t psmem = decode_persistent_smem_bytes<FG_HEAD_DIM>();
+    auto pkern = attention_decode_persistent_kernel<FG_HEAD_DIM>;
+    static bool pattr_set = false;
+    if (!pattr_set) {
+      cudaError_t e = cudaFuncSetAttribute(pkern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+      FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
+      pattr_set = true;
+    }
+    fg_launch_pdl(pkern, dim3(n_sms), dim3(PS_THREADS), psmem, stream, km, vm, layer, (const __nv_bfloat16*)q,
+                  q_stride, block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_seqs, n_heads,
+                  n_kv_heads, group, window, scale * 1.4426950408889634f, scratch, max_splits, status);
+  } else {
+    dim3 grid(max_splits, n_kv_heads, n_seqs);
+    fg_launch_pdl(kern, grid, dim3(THREADS), smem, stream, km, vm, layer, (const __nv_bfloat16*)q, q_stride,
+                  block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_heads, group, window,
+                  scale * 1.4426950408889634f, scratch, max_splits, status);
+  }
   FG_CHECK_LAUNCH("fg_attention_decode_tma_bf16");
   dim3 cgrid(n_heads, n_seqs);
   fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(128), 0, stream,

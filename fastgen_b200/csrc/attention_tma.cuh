@@ -252,6 +252,224 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
 
 
 // ---------------------------------------------------------------------------------
+// single tokens, persistent: a producer warp streams the splits' keys and values
+// through two shared-memory stages while four consumer warps work on the stage
+// before, so the memory system never waits for the arithmetic
+// ---------------------------------------------------------------------------------
+constexpr int PS_THREADS = 160;  // 4 consumer warps + 1 producer warp
+constexpr int PS_CONSUMERS = 128;
+
+template <int HD>
+constexpr size_t decode_persistent_smem_bytes() {
+  // two stages of keys and values, the merge buffer of the four warps, alignment slack
+  return (size_t)2 * 2 * SPLIT * HD * 2 + (size_t)4 * DECODE_ROWS * (HD + 2) * 4 + 1024;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PS_THREADS)
+attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
+                                   const __grid_constant__ CUtensorMap v_map, int layer,
+                                   const __nv_bfloat16* __restrict__ q, int q_stride,
+                                   const int* __restrict__ block_table, int table_width, int page_size,
+                                   int n_pages, const int* __restrict__ pos, const int* __restrict__ seq_req,
+                                   const int* __restrict__ seq_tok, int n_seqs, int n_heads, int n_kv_heads,
+                                   int group, int window, float scale_log2, float* __restrict__ scratch,
+                                   int max_splits, int* status) {
+  static_assert(HD % 64 == 0, "tiled loads take 64-element halves");
+  constexpr int NT = 4;
+  constexpr int HALVES = HD / 64;
+  constexpr int STAGE_BYTES = HALVES * HALF_BYTES;  // keys (or values) of one split
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  unsigned char* Ks = smem;                       // [2 stages][HALVES][SPLIT rows][128 B]
+  unsigned char* Vs = Ks + 2 * STAGE_BYTES;
+  float* wo = reinterpret_cast<float*>(Vs + 2 * STAGE_BYTES);  // [4 warps][16 rows][HD]
+  float* wm = wo + 4 * DECODE_ROWS * HD;                        // [4][16] max
+  float* wl = wm + 4 * DECODE_ROWS;                             // [4][16] sum
+  __shared__ __align__(8) uint64_t full_k[2], full_v[2], empty[2];
+
+  pdl_trigger();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    for (int s2 = 0; s2 < 2; ++s2) {
+      mbar_init(&full_k[s2], 1);
+      mbar_init(&full_v[s2], 1);
+      mbar_init(&empty[s2], 4);  // one arrival a consumer warp
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_wait();
+
+  const int box_rows = min(page_size, SPLIT);
+  const int n_boxes = SPLIT / box_rows;
+  const int total = n_seqs * n_kv_heads * max_splits;
+  // An item is (sequence, kv head, split).  The splits of one (sequence, head) are
+  // spread over the blocks.  Both kinds of warps walk the same list and skip the same
+  // items (those beyond the request's keys or before its window).
+  auto decode = [&](int item, int& seq, int& g, int& split, int& p, int& k_begin) -> bool {
+    split = item % max_splits;
+    const int rest = item / max_splits;
+    g = rest % n_kv_heads;
+    seq = rest / n_kv_heads;
+    if (seq_req[seq] < 0) return false;
+    p = pos[seq_tok[seq]];
+    const int k0 = split * SPLIT;
+    if (k0 > p) return false;
+    k_begin = window > 0 ? max(0, p - window + 1) : 0;
+    return k0 + SPLIT > k_begin;
+  };
+
+  if (warp == 4) {
+    // ================================ producer ================================
+    int n_done = 0;
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+      int seq, g, split, p, k_begin;
+      if (!decode(item, seq, g, split, p, k_begin)) continue;
+      const int stage = n_done & 1;
+      if (n_done >= 2) mbar_wait(&empty[stage], ((n_done >> 1) - 1) & 1, status);
+      const int k0 = split * SPLIT, k_end = p + 1;
+      const int b = seq_req[seq];
+      // pages of the split's boxes: lane i looks up box i
+      int page = -1;
+      if (lane < n_boxes) {
+        const int j0 = k0 + lane * box_rows;
+        if (j0 < k_end && j0 + box_rows > k_begin) {
+          const int logical = j0 / page_size;
+          page = logical < table_width ? block_table[(size_t)b * table_width + logical] : -1;
+          if (page < 0 || page >= n_pages) {
+            page = -1;
+            if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+          }
+        }
+      }
+      const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
+      // boxes with nothing to load hold zeros (a masked probability times garbage could be NaN)
+      bool zeroed = false;
+      for (int i = 0; i < n_boxes; ++i) {
+        if (valid & (1u << i)) continue;
+        zeroed = true;
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int h = 0; h < HALVES; ++h)
+          for (int c = lane; c < box_rows * 8; c += 32) {
+            *reinterpret_cast<uint4*>(Ks + stage * STAGE_BYTES + h * HALF_BYTES + i * box_rows * 128 + c * 16) = z;
+            *reinterpret_cast<uint4*>(Vs + stage * STAGE_BYTES + h * HALF_BYTES + i * box_rows * 128 + c * 16) = z;
+          }
+      }
+      if (zeroed) {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+      }
+      const int bytes = __popc(valid) * box_rows * HD * 2;
+      const int slot0 = k0 % page_size;
+      if (lane == 0) {
+        mbar_arrive_expect(&full_k[stage], bytes);
+        mbar_arrive_expect(&full_v[stage], bytes);
+      }
+      __syncwarp();
+      // lane i issues box i's copies: keys first (the scores need them first)
+      if (page >= 0) {
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_5d(Ks + stage * STAGE_BYTES + h * HALF_BYTES + lane * box_rows * 128, &k_map, h * 64, slot0, g,
+                      page, layer, &full_k[stage]);
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_5d(Vs + stage * STAGE_BYTES + h * HALF_BYTES + lane * box_rows * 128, &v_map, h * 64, slot0, g,
+                      page, layer, &full_v[stage]);
+      }
+      ++n_done;
+    }
+  } else {
+    // ================================ consumers ================================
+    int n_done = 0;
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+      int seq, g, split, p, k_begin;
+      if (!decode(item, seq, g, split, p, k_begin)) continue;
+      const int stage = n_done & 1, parity = (n_done >> 1) & 1;
+      const int k0 = split * SPLIT, k_end = p + 1;
+      const int tok = seq_tok[seq];
+      // this thread's pieces of the queries, straight from global memory in the A-fragment
+      // layout: rows lane/4 and lane/4 + 8, columns 2*(lane%4) and +8; rows beyond the group are zero
+      uint32_t qf[HD / 16][4];
+      {
+        const int r = lane >> 2, c2 = (lane & 3) * 2;
+        const __nv_bfloat16* q0 = q + (size_t)tok * q_stride + (g * group + r) * HD + c2;
+        const __nv_bfloat16* q1 = q0 + 8 * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          qf[kk][0] = r < group ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16) : 0u;
+          qf[kk][2] = r < group ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8) : 0u;
+          qf[kk][1] = r + 8 < group ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16) : 0u;
+          qf[kk][3] = r + 8 < group ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8) : 0u;
+        }
+      }
+      mbar_wait(&full_k[stage], parity, status);
+      float s[NT][4];
+      qk_product_swz<HD, NT>(s, qf, Ks + stage * STAGE_BYTES, warp * 32, lane);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = k0 + warp * 32 + nt * 8 + 2 * (lane & 3) + (e & 1);
+          const bool vis = j >= k_begin && j < k_end;
+          s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+        }
+      float o[HD / 8][4];
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+      softmax_step<HD, NT>(s, o, m, l);
+      mbar_wait(&full_v[stage], parity, status);
+      pv_product_swz<HD, NT>(o, s, Vs + stage * STAGE_BYTES, warp * 32, lane);
+      // this warp is done with the stage: the producer may refill it
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[stage]);
+
+      // merge the four warps (rows that hold heads only)
+      const int r0 = lane >> 2;
+      if ((lane & 3) == 0) {
+        wm[warp * DECODE_ROWS + r0] = m[0];
+        wm[warp * DECODE_ROWS + r0 + 8] = m[1];
+        wl[warp * DECODE_ROWS + r0] = l[0];
+        wl[warp * DECODE_ROWS + r0 + 8] = l[1];
+      }
+#pragma unroll
+      for (int nt = 0; nt < HD / 8; ++nt) {
+        const int d = nt * 8 + 2 * (lane & 3);
+        if (r0 < group)
+          *reinterpret_cast<float2*>(wo + (warp * DECODE_ROWS + r0) * HD + d) = make_float2(o[nt][0], o[nt][1]);
+        if (r0 + 8 < group)
+          *reinterpret_cast<float2*>(wo + (warp * DECODE_ROWS + r0 + 8) * HD + d) = make_float2(o[nt][2], o[nt][3]);
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(PS_CONSUMERS) : "memory");
+      for (int i = tid; i < group * HD; i += PS_CONSUMERS) {
+        const int r = i / HD, d = i - r * HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, wm[w * DECODE_ROWS + r]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float mw = wm[w * DECODE_ROWS + r];
+          const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+          acc += f * wo[(w * DECODE_ROWS + r) * HD + d];
+          ll += f * wl[w * DECODE_ROWS + r];
+        }
+        float* dst = scratch + (((size_t)seq * n_heads + g * group + r) * max_splits + split) * part_stride<HD>();
+        dst[d] = acc;
+        if (d == 0) {
+          dst[HD] = mm;
+          dst[HD + 1] = ll;
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(PS_CONSUMERS) : "memory");  // the merge buffer is free again
+      ++n_done;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // prompt portions with tiled TMA loads
 // ---------------------------------------------------------------------------------
 constexpr int PF_ROWS = 128;   // query rows per block (8 warps x 16)

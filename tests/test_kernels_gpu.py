@@ -327,6 +327,13 @@ CASES = [
     ([(0, 300), (190, 75), (63, 2), (7, 130)], 8, 2, 64, 8, None),     # prompt portions, small pages
     ([(100, 200), (0, 129)], 6, 2, 128, 16, 90),                        # ... with a window
     ([(250, 260)], 4, 1, 128, 256, None),
+    # enough (request, head, split) items for the persistent single-token kernel
+    ([(900, 1), (130, 1), (767, 1), (768, 1), (5, 1), (640, 1), (899, 1), (0, 1), (127, 1), (128, 1), (511, 1),
+      (333, 1)], 32, 8, 128, 64, None),
+    ([(900, 1), (130, 1), (767, 1), (768, 1), (5, 1), (640, 1), (899, 1), (0, 1), (127, 1), (128, 1), (511, 1),
+      (333, 1), (40, 30)], 16, 8, 128, 16, 300),
+    ([(1500 + 37 * i, 1) for i in range(10)] + [(3 + 129 * i, 1) for i in range(10)], 20, 2, 64, 8, None),
+    ([(1500, 1), (255, 1), (256, 1), (1023, 1), (1024, 1), (700, 1), (1, 1), (1300, 1)], 8, 8, 128, 256, None),
 ]
 
 
