@@ -206,16 +206,16 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  if (items >= 4 * n_sms) {
-    constexpr size_t psmem = decode_persistent_smem_bytes<FG_HEAD_DIM>();
+  const size_t psmem = decode_persistent_smem_bytes<FG_HEAD_DIM>(group);
+  if (items >= 4 * n_sms && group <= PS_MAX_GROUP && psmem <= 227 * 1024 - 256) {
     auto pkern = attention_decode_persistent_kernel<FG_HEAD_DIM>;
-    static bool pattr_set = false;
-    if (!pattr_set) {
+    static size_t pattr_set = 0;
+    if (pattr_set < psmem) {
       cudaError_t e = cudaFuncSetAttribute(pkern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
       FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
-      pattr_set = true;
+      pattr_set = psmem;
     }
-    fg_launch_pdl(pkern, dim3(n_sms), dim3(PS_THREADS), psmem, stream, km, vm, layer, (const __nv_bfloat16*)q,
+    fg_launch_pdl(pkern, dim3(2 * n_sms), dim3(PS_THREADS), psmem, stream, km, vm, layer, (const __nv_bfloat16*)q,
                   q_stride, block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_seqs, n_heads,
                   n_kv_heads, group, window, scale * 1.4426950408889634f, scratch, max_splits, status);
   } else {

@@ -252,21 +252,37 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
 
 
 // ---------------------------------------------------------------------------------
-// single tokens, persistent: a producer warp streams the splits' keys and values
-// through two shared-memory stages while four consumer warps work on the stage
-// before, so the memory system never waits for the arithmetic
+// single tokens, persistent: blocks stay on their SM and walk a list of (request, kv
+// head, split) items.  A producer warp streams the items' keys and values through a ring
+// of shared-memory slots (keys and values of a split take a slot each) while four
+// consumer warps work on the slots before, so page look-ups, launch ramps and the merge
+// of the warps hide behind the loads.  The products are taken transposed: keys (or value
+// columns) are the 16-row operand and the group's heads the 8-column one, so a group of
+// up to 8 heads wastes half of a tile instead of three quarters.
 // ---------------------------------------------------------------------------------
 constexpr int PS_THREADS = 160;  // 4 consumer warps + 1 producer warp
 constexpr int PS_CONSUMERS = 128;
+constexpr int PS_SLOTS = 3;
+constexpr int PS_MAX_GROUP = 8;
 
 template <int HD>
-constexpr size_t decode_persistent_smem_bytes() {
-  // two stages of keys and values, the merge buffer of the four warps, alignment slack
-  return (size_t)2 * 2 * SPLIT * HD * 2 + (size_t)4 * DECODE_ROWS * (HD + 2) * 4 + 1024;
+__host__ __device__ constexpr int ps_merge_ld() { return HD + 4; }  // rows of the merge buffer fall on different banks
+
+template <int HD>
+inline size_t decode_persistent_smem_bytes(int group) {
+  // the ring, the merge buffer of the four warps (values, maxima, sums), alignment slack
+  return (size_t)PS_SLOTS * SPLIT * HD * 2 + (size_t)4 * group * ps_merge_ld<HD>() * 4 + 2 * 4 * PS_MAX_GROUP * 4 +
+         1024;
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
 }
 
 template <int HD>
-__global__ void __launch_bounds__(PS_THREADS)
+__global__ void __launch_bounds__(PS_THREADS, 2)
 attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
                                    const __grid_constant__ CUtensorMap v_map, int layer,
                                    const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -276,25 +292,23 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
                                    int group, int window, float scale_log2, float* __restrict__ scratch,
                                    int max_splits, int* status) {
   static_assert(HD % 64 == 0, "tiled loads take 64-element halves");
-  constexpr int NT = 4;
   constexpr int HALVES = HD / 64;
-  constexpr int STAGE_BYTES = HALVES * HALF_BYTES;  // keys (or values) of one split
+  constexpr int SLOT_BYTES = HALVES * HALF_BYTES;  // keys (or values) of one split
+  constexpr int MLD = ps_merge_ld<HD>();
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
-  unsigned char* Ks = smem;                       // [2 stages][HALVES][SPLIT rows][128 B]
-  unsigned char* Vs = Ks + 2 * STAGE_BYTES;
-  float* wo = reinterpret_cast<float*>(Vs + 2 * STAGE_BYTES);  // [4 warps][16 rows][HD]
-  float* wm = wo + 4 * DECODE_ROWS * HD;                        // [4][16] max
-  float* wl = wm + 4 * DECODE_ROWS;                             // [4][16] sum
-  __shared__ __align__(8) uint64_t full_k[2], full_v[2], empty[2];
+  unsigned char* ring = smem;                                              // [PS_SLOTS][HALVES][SPLIT rows][128 B]
+  float* wo = reinterpret_cast<float*>(ring + PS_SLOTS * SLOT_BYTES);      // [4 warps][group][MLD]
+  float* wm = wo + 4 * group * MLD;                                        // [4][8] maxima
+  float* wl = wm + 4 * PS_MAX_GROUP;                                       // [4][8] sums
+  __shared__ __align__(8) uint64_t full[PS_SLOTS], empty[PS_SLOTS];
 
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
-    for (int s2 = 0; s2 < 2; ++s2) {
-      mbar_init(&full_k[s2], 1);
-      mbar_init(&full_v[s2], 1);
-      mbar_init(&empty[s2], 4);  // one arrival a consumer warp
+    for (int i = 0; i < PS_SLOTS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 4);  // one arrival a consumer warp
     }
     mbar_fence_init();
   }
@@ -304,10 +318,9 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
   const int box_rows = min(page_size, SPLIT);
   const int n_boxes = SPLIT / box_rows;
   const int total = n_seqs * n_kv_heads * max_splits;
-  // An item is (sequence, kv head, split).  The splits of one (sequence, head) are
-  // spread over the blocks.  Both kinds of warps walk the same list and skip the same
-  // items (those beyond the request's keys or before its window).
-  auto decode = [&](int item, int& seq, int& g, int& split, int& p, int& k_begin) -> bool {
+  // Both kinds of warps walk the same list and skip the same items (padding lanes,
+  // splits beyond the request's keys or before its window).
+  auto item_of = [&](int item, int& seq, int& g, int& split, int& p, int& k_begin) -> bool {
     split = item % max_splits;
     const int rest = item / max_splits;
     g = rest % n_kv_heads;
@@ -322,12 +335,10 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
 
   if (warp == 4) {
     // ================================ producer ================================
-    int n_done = 0;
+    int n_fill = 0;  // fills so far: item i's keys are fill 2i, its values fill 2i + 1
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       int seq, g, split, p, k_begin;
-      if (!decode(item, seq, g, split, p, k_begin)) continue;
-      const int stage = n_done & 1;
-      if (n_done >= 2) mbar_wait(&empty[stage], ((n_done >> 1) - 1) & 1, status);
+      if (!item_of(item, seq, g, split, p, k_begin)) continue;
       const int k0 = split * SPLIT, k_end = p + 1;
       const int b = seq_req[seq];
       // pages of the split's boxes: lane i looks up box i
@@ -344,117 +355,166 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
         }
       }
       const unsigned valid = __ballot_sync(0xffffffffu, page >= 0);
-      // boxes with nothing to load hold zeros (a masked probability times garbage could be NaN)
-      bool zeroed = false;
-      for (int i = 0; i < n_boxes; ++i) {
-        if (valid & (1u << i)) continue;
-        zeroed = true;
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int h = 0; h < HALVES; ++h)
-          for (int c = lane; c < box_rows * 8; c += 32) {
-            *reinterpret_cast<uint4*>(Ks + stage * STAGE_BYTES + h * HALF_BYTES + i * box_rows * 128 + c * 16) = z;
-            *reinterpret_cast<uint4*>(Vs + stage * STAGE_BYTES + h * HALF_BYTES + i * box_rows * 128 + c * 16) = z;
-          }
-      }
-      if (zeroed) {
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        __syncwarp();
-      }
       const int bytes = __popc(valid) * box_rows * HD * 2;
-      const int slot0 = k0 % page_size;
-      if (lane == 0) {
-        mbar_arrive_expect(&full_k[stage], bytes);
-        mbar_arrive_expect(&full_v[stage], bytes);
-      }
-      __syncwarp();
-      // lane i issues box i's copies: keys first (the scores need them first)
-      if (page >= 0) {
+      const int slot0 = k0 % page_size;  // 0 unless pages are longer than a split
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_5d(Ks + stage * STAGE_BYTES + h * HALF_BYTES + lane * box_rows * 128, &k_map, h * 64, slot0, g,
-                      page, layer, &full_k[stage]);
+      for (int kv = 0; kv < 2; ++kv) {
+        const int slot = n_fill % PS_SLOTS;
+        if (n_fill >= PS_SLOTS) mbar_wait(&empty[slot], (n_fill / PS_SLOTS - 1) & 1, status);
+        unsigned char* dst = ring + slot * SLOT_BYTES;
+        // boxes with nothing to load hold zeros (a masked probability times garbage could be NaN)
+        if (valid != (n_boxes >= 32 ? 0xffffffffu : (1u << n_boxes) - 1u)) {
+          for (int i = 0; i < n_boxes; ++i) {
+            if (valid & (1u << i)) continue;
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int h = 0; h < HALVES; ++h)
+              for (int c = lane; c < box_rows * 8; c += 32)
+                *reinterpret_cast<uint4*>(dst + h * HALF_BYTES + i * box_rows * 128 + c * 16) = z;
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_expect(&full[slot], bytes);
+        __syncwarp();
+        if (page >= 0) {  // lane i issues box i's copies
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_5d(Vs + stage * STAGE_BYTES + h * HALF_BYTES + lane * box_rows * 128, &v_map, h * 64, slot0, g,
-                      page, layer, &full_v[stage]);
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_5d(dst + h * HALF_BYTES + lane * box_rows * 128, kv ? &v_map : &k_map, h * 64, slot0, g, page,
+                        layer, &full[slot]);
+        }
+        ++n_fill;
       }
-      ++n_done;
     }
   } else {
     // ================================ consumers ================================
-    int n_done = 0;
+    int n_item = 0;
+    const int hq = lane >> 2, qd = (lane & 3) * 2;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       int seq, g, split, p, k_begin;
-      if (!decode(item, seq, g, split, p, k_begin)) continue;
-      const int stage = n_done & 1, parity = (n_done >> 1) & 1;
+      if (!item_of(item, seq, g, split, p, k_begin)) continue;
       const int k0 = split * SPLIT, k_end = p + 1;
       const int tok = seq_tok[seq];
-      // this thread's pieces of the queries, straight from global memory in the A-fragment
-      // layout: rows lane/4 and lane/4 + 8, columns 2*(lane%4) and +8; rows beyond the group are zero
-      uint32_t qf[HD / 16][4];
+      // the queries as the 8-column operand, straight from global memory: column lane/4 is
+      // a head of the group (zero beyond it), rows 2*(lane%4), +1 and +8, +9 of each 16 dims
+      uint32_t qb[HD / 16][2];
       {
-        const int r = lane >> 2, c2 = (lane & 3) * 2;
-        const __nv_bfloat16* q0 = q + (size_t)tok * q_stride + (g * group + r) * HD + c2;
-        const __nv_bfloat16* q1 = q0 + 8 * HD;
+        const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (g * group + hq) * HD + qd;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          qf[kk][0] = r < group ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16) : 0u;
-          qf[kk][2] = r < group ? *reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8) : 0u;
-          qf[kk][1] = r + 8 < group ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16) : 0u;
-          qf[kk][3] = r + 8 < group ? *reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8) : 0u;
+          qb[kk][0] = hq < group ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16) : 0u;
+          qb[kk][1] = hq < group ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8) : 0u;
         }
       }
-      mbar_wait(&full_k[stage], parity, status);
-      float s[NT][4];
-      qk_product_swz<HD, NT>(s, qf, Ks + stage * STAGE_BYTES, warp * 32, lane);
+      const int fk = 2 * n_item, fv = fk + 1;
+      const int slot_k = fk % PS_SLOTS, slot_v = fv % PS_SLOTS;
+      const unsigned char* Ks = ring + slot_k * SLOT_BYTES;
+      const unsigned char* Vs = ring + slot_v * SLOT_BYTES;
+
+      // S^T[keys, heads] = K Q^T for this warp's 32 keys
+      mbar_wait(&full[slot_k], (fk / PS_SLOTS) & 1, status);
+      float s[2][4];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+      for (int mt = 0; mt < 2; ++mt) {
+        s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+        const int row = warp * 32 + mt * 16 + (lane & 15);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          uint32_t a[4];
+          ldmatrix_x4(a, Ks + (kk >> 2) * HALF_BYTES + swz(row, (kk & 3) * 2 + (lane >> 4)));
+          mma_16816(s[mt], a, qb[kk][0], qb[kk][1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[slot_k]);  // this warp is done with the keys
+
+      // softmax over the warp's keys, per head: this thread holds heads qd and qd + 1
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int j = k0 + warp * 32 + nt * 8 + 2 * (lane & 3) + (e & 1);
+          const int j = k0 + warp * 32 + mt * 16 + hq + ((e & 2) ? 8 : 0);
           const bool vis = j >= k_begin && j < k_end;
-          s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
+          s[mt][e] = vis ? s[mt][e] * scale_log2 : -INFINITY;
+          mx[e & 1] = fmaxf(mx[e & 1], s[mt][e]);
         }
-      float o[HD / 8][4];
+      float sum[2] = {0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-      float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-      softmax_step<HD, NT>(s, o, m, l);
-      mbar_wait(&full_v[stage], parity, status);
-      pv_product_swz<HD, NT>(o, s, Vs + stage * STAGE_BYTES, warp * 32, lane);
-      // this warp is done with the stage: the producer may refill it
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[stage]);
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          // the probabilities are rounded to bfloat16 for the product; sum what is used
+          const float pr = mx[e & 1] == -INFINITY
+                               ? 0.f
+                               : __bfloat162float(__float2bfloat16_rn(exp2f(s[mt][e] - mx[e & 1])));
+          s[mt][e] = pr;
+          sum[e & 1] += pr;
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 4);
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 8);
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 16);
+      }
+      // P^T as the 8-column operand: an 8x8 transpose in registers for each half tile
+      uint32_t pb[2][2];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        pb[mt][0] = movmatrix_trans(pack_bf16(s[mt][0], s[mt][1]));
+        pb[mt][1] = movmatrix_trans(pack_bf16(s[mt][2], s[mt][3]));
+      }
 
-      // merge the four warps (rows that hold heads only)
-      const int r0 = lane >> 2;
-      if ((lane & 3) == 0) {
-        wm[warp * DECODE_ROWS + r0] = m[0];
-        wm[warp * DECODE_ROWS + r0 + 8] = m[1];
-        wl[warp * DECODE_ROWS + r0] = l[0];
-        wl[warp * DECODE_ROWS + r0 + 8] = l[1];
+      // O^T[dims, heads] = V^T P^T
+      mbar_wait(&full[slot_v], (fv / PS_SLOTS) & 1, status);
+      float o[HD / 16][4];
+#pragma unroll
+      for (int dt = 0; dt < HD / 16; ++dt) {
+        o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          const int key = warp * 32 + ks * 16 + ((lane >> 4) << 3) + (lane & 7);
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, Vs + (dt >> 2) * HALF_BYTES + swz(key, (dt & 3) * 2 + ((lane >> 3) & 1)));
+          mma_16816(o[dt], a, pb[ks][0], pb[ks][1]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[slot_v]);  // ... and with the values
+
+      // merge the four warps (heads of the group only)
+      if (hq == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          wm[warp * PS_MAX_GROUP + qd + h] = mx[h];
+          wl[warp * PS_MAX_GROUP + qd + h] = sum[h];
+        }
       }
 #pragma unroll
-      for (int nt = 0; nt < HD / 8; ++nt) {
-        const int d = nt * 8 + 2 * (lane & 3);
-        if (r0 < group)
-          *reinterpret_cast<float2*>(wo + (warp * DECODE_ROWS + r0) * HD + d) = make_float2(o[nt][0], o[nt][1]);
-        if (r0 + 8 < group)
-          *reinterpret_cast<float2*>(wo + (warp * DECODE_ROWS + r0 + 8) * HD + d) = make_float2(o[nt][2], o[nt][3]);
-      }
+      for (int dt = 0; dt < HD / 16; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int head = qd + (e & 1), d = dt * 16 + hq + ((e & 2) ? 8 : 0);
+          if (head < group) wo[(warp * group + head) * MLD + d] = o[dt][e];
+        }
       asm volatile("bar.sync 1, %0;\n" ::"n"(PS_CONSUMERS) : "memory");
       for (int i = tid; i < group * HD; i += PS_CONSUMERS) {
         const int r = i / HD, d = i - r * HD;
         float mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, wm[w * DECODE_ROWS + r]);
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, wm[w * PS_MAX_GROUP + r]);
         float acc = 0.f, ll = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          const float mw = wm[w * DECODE_ROWS + r];
+          const float mw = wm[w * PS_MAX_GROUP + r];
           const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-          acc += f * wo[(w * DECODE_ROWS + r) * HD + d];
-          ll += f * wl[w * DECODE_ROWS + r];
+          acc += f * wo[(w * group + r) * MLD + d];
+          ll += f * wl[w * PS_MAX_GROUP + r];
         }
         float* dst = scratch + (((size_t)seq * n_heads + g * group + r) * max_splits + split) * part_stride<HD>();
         dst[d] = acc;
@@ -464,7 +524,7 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
         }
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(PS_CONSUMERS) : "memory");  // the merge buffer is free again
-      ++n_done;
+      ++n_item;
     }
   }
 }
