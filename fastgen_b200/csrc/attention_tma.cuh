@@ -143,7 +143,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     mbar_fence_init();
   }
   __syncthreads();
-  pdl_wait();
+  // The step's own kernels write keys and values at the tokens' positions only, so a
+  // split that ends before this token's position is loaded without waiting for them.
+  const bool early = k0 + SPLIT <= p;
+  if (!early) pdl_wait();
 
   if (tid == 0) {
     int n_valid = 0;
@@ -175,6 +178,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         *reinterpret_cast<uint4*>(Vs + h * HALF_BYTES + i * box_rows * 128 + c * 16) = z;
       }
   }
+  if (early) pdl_wait();  // the queries come from the kernel before
   constexpr int CH = HD / 8;
   for (int i = tid; i < DECODE_ROWS * CH; i += THREADS) {
     const int r = i / CH, c = i - r * CH;
@@ -313,7 +317,10 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
     mbar_fence_init();
   }
   __syncthreads();
-  pdl_wait();
+  // The step's own kernels write keys and values at the tokens' positions only: the
+  // producer loads splits that end before the token's position without waiting for the
+  // kernel before this one, and waits once it meets a split that holds the position.
+  // The consumers wait before they read the queries.
 
   const int box_rows = min(page_size, SPLIT);
   const int n_boxes = SPLIT / box_rows;
@@ -336,10 +343,15 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
   if (warp == 4) {
     // ================================ producer ================================
     int n_fill = 0;  // fills so far: item i's keys are fill 2i, its values fill 2i + 1
+    bool waited = false;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
       int seq, g, split, p, k_begin;
       if (!item_of(item, seq, g, split, p, k_begin)) continue;
       const int k0 = split * SPLIT, k_end = p + 1;
+      if (!waited && k0 + SPLIT > p) {
+        pdl_wait();
+        waited = true;
+      }
       const int b = seq_req[seq];
       // pages of the split's boxes: lane i looks up box i
       int page = -1;
@@ -385,8 +397,10 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
         ++n_fill;
       }
     }
+    if (!waited) pdl_wait();
   } else {
     // ================================ consumers ================================
+    pdl_wait();
     int n_item = 0;
     const int hq = lane >> 2, qd = (lane & 3) * 2;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
