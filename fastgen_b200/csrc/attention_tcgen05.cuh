@@ -6,10 +6,11 @@
 // A block owns 128 query rows (consecutive tokens of one request x the query
 // heads of one key/value head) and walks the request's keys in tiles of 64:
 //
-//   control warp:   TMA(K_t+1, V_t+1);  S_{t+1} = Q K_{t+1}^T  (tcgen05.mma, M128 N64 K16 x HD/16)
+//   load warp:      TMA(K_t, V_t) into stage t & 1 as soon as S_{t-2} / O_{t-2} are done
+//   MMA warp:       S_{t+1} = Q K_{t+1}^T  (tcgen05.mma, M128 N64 K16 x HD/16, one thread)
 //   4 softmax warps: S_t from TMEM (one row a thread: no shuffles for max and sum),
 //                    p = 2^((s - m) c),  P_t (bf16) back into TMEM over S_t's columns
-//   control warp:   O += P_t V_t      (tcgen05.mma with A from TMEM, M128 N=HD K16 x 4)
+//   MMA warp:       O += P_t V_t      (tcgen05.mma with A from TMEM, M128 N=HD K16 x 4)
 //
 // The warps only meet at mbarriers (scores ready, probabilities ready, output
 // done), so the tensor core computes S_{t+1} and O_t while the softmax warps are
@@ -36,7 +37,8 @@ using fg_tma::tma_load_5d;
 constexpr int ROWS = 128;     // query rows a block
 constexpr int KEYS = 64;      // key positions a tile
 constexpr int SOFTMAX_THREADS = 128;
-constexpr int THREADS = 160;  // 4 softmax warps + 1 control warp
+constexpr int THREADS = 192;  // 4 softmax warps, a load warp, an MMA warp
+constexpr int LOAD_WARP = 4, MMA_WARP = 5;
 constexpr int KV_HALF = KEYS * 128;   // bytes of one 64-element half of a K or V tile
 constexpr int Q_HALF = ROWS * 128;    // ... of the Q tile
 constexpr float RESCALE_THRESHOLD = 8.f;  // in units of log2
@@ -262,8 +264,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int k_end = max_pos + 1;
   const int n_tiles = (k_end - k_lo + KEYS - 1) / KEYS;
 
-  if (!softmax_thread) {
-    // =============================== control warp ===============================
+  if (warp == LOAD_WARP) {
+    // ================================ load warp ================================
+    // Keys and values of tile t go to stage t & 1 as soon as that stage is free: the
+    // keys' once S_{t-2} is done, the values' once O_{t-2} is.
     const int* table_row = block_table + (size_t)b * table_width;
     const int box_rows = min(page_size, KEYS);
     const int n_boxes = KEYS / box_rows;
@@ -286,35 +290,30 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       }
       __syncwarp();
     };
-    auto box_page = [&](int t, int i) { return box_pages[(t % tiles_per_fill) * n_boxes + i]; };
     // bring tile t's keys (or values) into stage t & 1; boxes that hold no position of
     // the request are zero-filled instead (a masked probability times garbage could be NaN)
-    auto load_tile = [&](int t, bool values) {
+    auto load_tile = [&](int t, const int* pages, bool values) {
       const int stage = t & 1;
       unsigned char* base = (values ? Vs : Ks) + stage * STAGE_BYTES;
       uint64_t* bar = values ? &full_v[stage] : &full_k[stage];
       int n_valid = 0;
-      bool zeroed = false;
-      for (int i = 0; i < n_boxes; ++i) {
-        if (box_page(t, i) >= 0) {
-          ++n_valid;
-          continue;
+      for (int i = 0; i < n_boxes; ++i) n_valid += pages[i] >= 0;
+      if (n_valid < n_boxes) {
+        for (int i = 0; i < n_boxes; ++i) {
+          if (pages[i] >= 0) continue;
+          const uint4 z = make_uint4(0, 0, 0, 0);
+          for (int h = 0; h < HALVES; ++h)
+            for (int c = lane; c < box_rows * 8; c += 32)
+              *reinterpret_cast<uint4*>(base + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
         }
-        zeroed = true;
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int h = 0; h < HALVES; ++h)
-          for (int c = lane; c < box_rows * 8; c += 32)
-            *reinterpret_cast<uint4*>(base + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
-      }
-      if (zeroed) {
         fence_async_smem();
         __syncwarp();
       }
       if (lane == 0) {
         mbar_arrive_expect(bar, n_valid * box_rows * HD * 2);
-        const int slot = page_size > KEYS ? (k_lo + t * KEYS) % page_size : 0;
+        const int slot = (k_lo + t * KEYS) & (page_size - 1) & ~(KEYS - 1);  // 0 unless pages are longer than a tile
         for (int i = 0; i < n_boxes; ++i) {
-          const int page = box_page(t, i);
+          const int page = pages[i];
           if (page < 0) continue;
 #pragma unroll
           for (int h = 0; h < HALVES; ++h)
@@ -324,57 +323,50 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       }
       __syncwarp();
     };
-    // S[t & 1] = Q K_t^T
-    auto issue_s = [&](int t) {
-      const int stage = t & 1;
-      mbar_wait(&full_k[stage], (t >> 1) & 1, status);
-      tc_fence_after();
-      if (lane == 0) {
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint64_t a = smem_desc(Qs + (kk / 4) * Q_HALF + (kk % 4) * 32, 16);
-          const uint64_t bd = smem_desc(Ks + stage * STAGE_BYTES + (kk / 4) * KV_HALF + (kk % 4) * 32, 16);
-          umma_f16(tmem + COL_S0 + stage * KEYS, a, bd, IDESC_S, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&s_done[stage]);
-      }
-      __syncwarp();
-    };
-
-    fill_pages(0);
-    load_tile(0, false);
-    load_tile(0, true);
-    issue_s(0);
+    int staged = 0;  // tiles of the staged stretch that were loaded
     for (int t = 0; t < n_tiles; ++t) {
-      const int stage = t & 1;
-      if (t + 1 < n_tiles) {
-        if ((t + 1) % tiles_per_fill == 0) fill_pages(t + 1);
-        // the keys' stage was last read by S_{t-1}, which finished before S_t did
-        load_tile(t + 1, false);
-      }
-      if (t > 0) {
-        // O_{t-1} done: its values' stage and the columns of S_{t-1} / P_{t-1} are free
-        mbar_wait(&o_done, (t - 1) & 1, status);
+      if (staged == 0) fill_pages(t);
+      const int* pages = box_pages + staged * n_boxes;
+      if (t >= 2) mbar_wait(&s_done[t & 1], ((t - 2) >> 1) & 1, status);
+      load_tile(t, pages, false);
+      if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+      load_tile(t, pages, true);
+      if (++staged == tiles_per_fill) staged = 0;
+    }
+  } else if (warp == MMA_WARP) {
+    // ================================ MMA warp ================================
+    // One thread issues everything; products run in the order of issue, so S_{t+1}
+    // (which overwrites the columns of S_{t-1} / P_{t-1}) follows O_{t-1} by itself.
+    if (lane == 0) {
+      const uint64_t q_desc = smem_desc(Qs, 16), k_desc = smem_desc(Ks, 16), v_desc = smem_desc(Vs, KV_HALF);
+      auto issue_s = [&](int t) {
+        const int stage = t & 1;
+        mbar_wait(&full_k[stage], (t >> 1) & 1, status);
         tc_fence_after();
-      }
-      if (t + 1 < n_tiles) {
-        load_tile(t + 1, true);
-        issue_s(t + 1);
-      }
-      // all softmax threads have stored P_t (and rescaled O where needed)
-      mbar_wait(&p_ready[stage], (t >> 1) & 1, status);
-      mbar_wait(&full_v[stage], (t >> 1) & 1, status);
-      tc_fence_after();
-      if (lane == 0) {
+        const uint64_t kd = k_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int j = 0; j < KEYS / 16; ++j) {
-          const uint64_t bd = smem_desc(Vs + stage * STAGE_BYTES + j * 16 * 128, KV_HALF);
-          umma_f16_ts(tmem + COL_O, tmem + COL_S0 + stage * KEYS + j * 8, bd, IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16(tmem + COL_S0 + stage * KEYS, q_desc + (uint64_t)(((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4),
+                   kd + (uint64_t)(((kk / 4) * KV_HALF + (kk % 4) * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
+        umma_commit(&s_done[stage]);
+      };
+      issue_s(0);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int stage = t & 1;
+        if (t + 1 < n_tiles) issue_s(t + 1);
+        // all softmax threads have stored P_t (and rescaled O where needed)
+        mbar_wait(&p_ready[stage], (t >> 1) & 1, status);
+        mbar_wait(&full_v[stage], (t >> 1) & 1, status);
+        tc_fence_after();
+        const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
+#pragma unroll
+        for (int j = 0; j < KEYS / 16; ++j)
+          umma_f16_ts(tmem + COL_O, tmem + COL_S0 + stage * KEYS + j * 8, vd + (uint64_t)((j * 16 * 128) >> 4),
+                      IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
         umma_commit(&o_done);
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // =============================== softmax warps ===============================
     const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
