@@ -324,14 +324,50 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       __syncwarp();
     };
     int staged = 0;  // tiles of the staged stretch that were loaded
-    for (int t = 0; t < n_tiles; ++t) {
-      if (staged == 0) fill_pages(t);
-      const int* pages = box_pages + staged * n_boxes;
-      if (t >= 2) mbar_wait(&s_done[t & 1], ((t - 2) >> 1) & 1, status);
-      load_tile(t, pages, false);
-      if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
-      load_tile(t, pages, true);
-      if (++staged == tiles_per_fill) staged = 0;
+    if (n_boxes == 1) {
+      // pages at least as long as a tile: one box a tile, and one lane does everything
+      // between the page look-ups (a single thread's instruction stream is what bounds
+      // this warp, so the loop is kept short)
+      const uint32_t k_bytes = KEYS * HD * 2;
+      for (int t = 0; t < n_tiles; ++t) {
+        if (staged == 0) fill_pages(t);
+        const int page = box_pages[staged];
+        const int stage = t & 1;
+        if (page >= 0) {
+          if (lane == 0) {
+            const int slot = (k_lo + t * KEYS) & (page_size - 1);
+            unsigned char* kb = Ks + stage * STAGE_BYTES;
+            unsigned char* vb = Vs + stage * STAGE_BYTES;
+            if (t >= 2) mbar_wait(&s_done[stage], ((t - 2) >> 1) & 1, status);
+            mbar_arrive_expect(&full_k[stage], k_bytes);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_5d(kb + h * KV_HALF, &k_map, h * 64, slot, g, page, layer, &full_k[stage]);
+            if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+            mbar_arrive_expect(&full_v[stage], k_bytes);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_5d(vb + h * KV_HALF, &v_map, h * 64, slot, g, page, layer, &full_v[stage]);
+          }
+        } else {
+          if (t >= 2) mbar_wait(&s_done[stage], ((t - 2) >> 1) & 1, status);
+          load_tile(t, box_pages + staged, false);
+          if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+          load_tile(t, box_pages + staged, true);
+        }
+        if (++staged == tiles_per_fill) staged = 0;
+        __syncwarp();  // the lanes stay together (the staged pages are replaced by all of them)
+      }
+    } else {
+      for (int t = 0; t < n_tiles; ++t) {
+        if (staged == 0) fill_pages(t);
+        const int* pages = box_pages + staged * n_boxes;
+        if (t >= 2) mbar_wait(&s_done[t & 1], ((t - 2) >> 1) & 1, status);
+        load_tile(t, pages, false);
+        if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+        load_tile(t, pages, true);
+        if (++staged == tiles_per_fill) staged = 0;
+      }
     }
   } else if (warp == MMA_WARP) {
     // ================================ MMA warp ================================
@@ -396,9 +432,17 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           if (!vis) s[i] = -INFINITY;
         }
       }
-      float mx = -INFINITY;
+      // four independent chains for the maximum (and below for the sum): a row is one
+      // thread's, and a single chain of 64 dependent operations would be all latency
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < KEYS; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 0; i < KEYS; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]);
+        mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]);
+        mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // raise the reference maximum only when it pays (or when there is none yet)
       float alpha = 1.f;
       bool raise = false;
@@ -414,12 +458,19 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
       } else {
         const float mc = m_ref * c;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < KEYS; i += 2) {
+        for (int i = 0; i < KEYS; i += 4) {
           const float p0 = exp2f(fmaf(s[i], c, -mc)), p1 = exp2f(fmaf(s[i + 1], c, -mc));
-          sum += p0 + p1;
+          const float p2 = exp2f(fmaf(s[i + 2], c, -mc)), p3 = exp2f(fmaf(s[i + 3], c, -mc));
+          sum4[0] += p0;
+          sum4[1] += p1;
+          sum4[2] += p2;
+          sum4[3] += p3;
           packed[i / 2] = pack_bf16(p0, p1);
+          packed[i / 2 + 1] = pack_bf16(p2, p3);
         }
+        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       }
       l_run = l_run * alpha + sum;
       // P_t over the first 32 columns of S_t (this thread has read all of its row)
