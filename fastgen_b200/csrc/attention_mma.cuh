@@ -539,7 +539,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 // request's splits, in ascending split order.  One block per (head, token).
 template <int HD>
 __global__ void __launch_bounds__(128)
-attention_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int out_stride,
+attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, int out_stride,
                          const int* __restrict__ pos, const int* __restrict__ seq_req,
                          const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
                          int* status) {

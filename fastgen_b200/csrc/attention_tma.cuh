@@ -89,7 +89,7 @@ constexpr size_t decode_tma_smem_bytes() {
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                            int layer, const __nv_bfloat16* __restrict__ q, int q_stride,
+                            int layer, const __nv_bfloat16* q, int q_stride,
                             const int* __restrict__ block_table, int table_width, int page_size, int n_pages,
                             const int* __restrict__ pos, const int* __restrict__ seq_req,
                             const int* __restrict__ seq_tok, int n_heads, int group, int window,
@@ -183,7 +183,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   for (int i = tid; i < DECODE_ROWS * CH; i += THREADS) {
     const int r = i / CH, c = i - r * CH;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < group) v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (g * group + r) * HD + c * 8);
+    if (r < group) v = ld_global_16(q + (size_t)tok * q_stride + (g * group + r) * HD + c * 8);
     *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
   }
   __syncthreads();
@@ -289,7 +289,7 @@ template <int HD>
 __global__ void __launch_bounds__(PS_THREADS, 2)
 attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
                                    const __grid_constant__ CUtensorMap v_map, int layer,
-                                   const __nv_bfloat16* __restrict__ q, int q_stride,
+                                   const __nv_bfloat16* q, int q_stride,
                                    const int* __restrict__ block_table, int table_width, int page_size,
                                    int n_pages, const int* __restrict__ pos, const int* __restrict__ seq_req,
                                    const int* __restrict__ seq_tok, int n_seqs, int n_heads, int n_kv_heads,
@@ -415,8 +415,8 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
         const __nv_bfloat16* qrow = q + (size_t)tok * q_stride + (g * group + hq) * HD + qd;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          qb[kk][0] = hq < group ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16) : 0u;
-          qb[kk][1] = hq < group ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8) : 0u;
+          qb[kk][0] = hq < group ? ld_global_4(qrow + kk * 16) : 0u;
+          qb[kk][1] = hq < group ? ld_global_4(qrow + kk * 16 + 8) : 0u;
         }
       }
       const int fk = 2 * n_item, fv = fk + 1;

@@ -47,11 +47,28 @@ void fg_set_error(const char* fmt, ...);
 // statement) lets the next kernel start early in turn, and pdl_wait() blocks until
 // the previous kernel has completed and its writes are visible.  Before pdl_wait() a
 // kernel may only touch what no earlier kernel of the step writes (weights, block
-// tables, positions) and must not write global memory.  Both are no-ops for a kernel
-// launched the ordinary way.  FG_NO_PDL=1 in the environment turns the attribute off.
+// tables, positions) and must not write global memory.  What an earlier kernel of the
+// step wrote must not be read through a `const __restrict__` pointer: the compiler may
+// move such a load above the wait (it takes the data for constant), and the kernel then
+// sees the previous step's values.  Such data is read through plain pointers or with
+// ld_global_16 / ld_global_4 below.  Both calls are no-ops for a kernel launched the
+// ordinary way.  FG_NO_PDL=1 in the environment turns the attribute off.
 // ---------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// Loads that stay where they are written (never hoisted above a wait, never through the
+// read-only cache).
+__device__ __forceinline__ uint4 ld_global_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_global_4(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 bool fg_pdl_enabled();
 

@@ -87,7 +87,7 @@ struct Ring {
 
 template <int NT, typename TO, int EPI>
 __global__ void __launch_bounds__(THREADS)
-gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
+gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
                    TO* __restrict__ y, int ldy, int M, int N, int K, QkvEpilogue qkv) {
   constexpr int PIECES = Ring<NT>::PIECES;
   constexpr int STAGES = Ring<NT>::STAGES;

@@ -78,8 +78,10 @@ constexpr int VEC_THREADS = 256;
 
 template <typename TH, typename TD, typename TO, int ITEMS>
 __global__ void __launch_bounds__(VEC_THREADS)
-rmsnorm_vec_kernel(TH* __restrict__ h, const TD* __restrict__ delta, const void* __restrict__ w, int w_dtype,
-                   TO* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
+rmsnorm_vec_kernel(TH* h, const TD* delta, const void* __restrict__ w, int w_dtype, TO* __restrict__ out,
+                   const int* __restrict__ rows, int dim, float eps) {
+  // h and delta come from earlier kernels of the step: no __restrict__, so that their
+  // loads stay below the wait
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();

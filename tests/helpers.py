@@ -13,7 +13,7 @@ import torch
 import plain_llama as pl
 from fastgen_b200.weights import write_random_model
 
-# Three tiny Llama configurations that differ in every size and option.
+# Tiny Llama configurations that differ in every size and option.
 TINY_A = dict(
     architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=176,
     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1,
@@ -38,7 +38,21 @@ TINY_C = dict(
                       original_max_position_embeddings=32),
     sliding_window=24, max_position_embeddings=384,
 )
-CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 2), "tiny_c": (TINY_C, 7)}
+# head sizes 64 and 128: the sizes whose bfloat16 attention runs on TMA tiles and tcgen05
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_size=344,
+    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+    rms_norm_eps=1e-5, vocab_size=300, tie_word_embeddings=False, rope_theta=10000.0,
+    max_position_embeddings=640,
+)
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=232, intermediate_size=264,
+    num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+    rms_norm_eps=1e-6, vocab_size=270, tie_word_embeddings=True, rope_theta=50000.0,
+    sliding_window=100, max_position_embeddings=512,
+)
+CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 2), "tiny_c": (TINY_C, 7), "tiny_d": (TINY_D, 11),
+           "tiny_e": (TINY_E, 13)}
 
 
 def make_model_dir(tmp_path, name: str, std: float = None) -> Path:

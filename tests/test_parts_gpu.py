@@ -276,6 +276,38 @@ def test_first_tokens(tmp_path, dtype):
     H.compare(model_dir, reqs, H.collect(steps, outputs), dtype)
 
 
+def test_many_key_splits_through_graphs(tmp_path):
+    """Four live requests with thousands of cached keys and eight key/value heads: enough
+    (request, head, split) items for the persistent single-token kernel, inside captured
+    graphs with programmatic dependent launch, where a load that is moved above the wait on
+    the kernel before would see the step before."""
+    cfg = dict(
+        architectures=["LlamaForCausalLM"], hidden_size=128, intermediate_size=136, num_hidden_layers=2,
+        num_attention_heads=16, num_key_value_heads=8, head_dim=64, rms_norm_eps=1e-5, vocab_size=211,
+        tie_word_embeddings=False, rope_theta=10000.0, max_position_embeddings=4096,
+    )
+    from fastgen_b200.weights import write_random_model
+    model_dir = write_random_model(tmp_path / "wide", cfg, seed=21, norm_jitter=0.1)
+    lengths = [2400, 2500, 2300, 2450]
+    tail = 5
+    reqs = {f"w{i}": H.random_tokens(211, n, 400 + i) for i, n in enumerate(lengths)}
+    steps = []
+    for rid, toks in reqs.items():
+        head = len(toks) - tail
+        steps.append(dict(step=len(steps), entries=[dict(id=rid, tokens=toks[:head], want=[head - 1])], end=[]))
+    for k in range(tail):
+        entries = [dict(id=rid, tokens=[toks[len(toks) - tail + k]], want=[0]) for rid, toks in reqs.items()]
+        steps.append(dict(step=len(steps), entries=entries, end=[]))
+    outputs, engine = H.run_engine(model_dir, torch.bfloat16, steps, page_size=64, max_tokens=4 * 2560)
+    assert engine.graphs is not None and engine.graphs.replays >= tail
+    got = H.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        ref = H.plain_logits(model_dir, toks)
+        for p, row in got[rid].items():
+            err = float(np.abs(row - ref[p]).max())
+            assert err <= 0.02 * max(1.0, float(np.abs(ref[p]).max())), (rid, p, err)
+
+
 # ---------------------------------------------------------------------------------
 # the sizes of a Llama-3.1-8B layer (two layers, a small vocabulary)
 # ---------------------------------------------------------------------------------

@@ -15,7 +15,7 @@ import helpers as H
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
-PAGES = {"tiny_a": 8, "tiny_b": 16, "tiny_c": 8}
+PAGES = {"tiny_a": 8, "tiny_b": 16, "tiny_c": 8, "tiny_d": 64, "tiny_e": 16}
 
 
 def _requests(name, lengths, seed):
@@ -23,7 +23,8 @@ def _requests(name, lengths, seed):
     return {f"r{i}": H.random_tokens(vocab, n, seed + i) for i, n in enumerate(lengths)}
 
 
-LENGTHS = {"tiny_a": [7, 13, 1, 30, 70], "tiny_b": [1, 9, 40, 64, 100], "tiny_c": [5, 33, 90, 64]}
+LENGTHS = {"tiny_a": [7, 13, 1, 30, 70], "tiny_b": [1, 9, 40, 64, 100], "tiny_c": [5, 33, 90, 64],
+           "tiny_d": [3, 70, 200, 129, 330], "tiny_e": [5, 150, 260, 64]}
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
