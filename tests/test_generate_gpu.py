@@ -97,6 +97,46 @@ def test_sampling_is_seeded_and_independent_of_batching(tmp_path):
         assert abs(float(lp[len(prompts[1]) - 1 + k, tok]) - together[1].logprobs[k]) < 1e-3
 
 
+def test_sync_freq_does_not_change_tokens(tmp_path):
+    """Runs of 1, 3, 10 or 64 decode steps between two reads of the sampled tokens give the
+    same tokens: greedy in bfloat16 at head size 64 (keys beyond one split), and sampled in
+    float32, with a stop token that falls inside a run."""
+    model_dir = H.make_model_dir(tmp_path, "tiny_d")
+    prompts = [H.random_tokens(300, n, 40 + i) for i, n in enumerate([3, 140, 70])]
+    ref = None
+    for freq in (1, 3, 10, 64):
+        out, _ = _generate(model_dir, prompts, torch.bfloat16, use_sampling=False, max_gen=40, cache_block=64,
+                           max_seq=1024, max_batch=4, sync_freq=freq)
+        toks = [out[i].tokens for i in range(len(prompts))]
+        assert all(len(t) == 40 for t in toks)
+        ref = ref or toks
+        assert toks == ref, f"sync_freq {freq}"
+
+    from fastgen_b200.engine import Fastgen, GenArgs, HfLoader, Packet
+    model_dir = H.make_model_dir(tmp_path, "tiny_b")
+    prompts = [H.random_tokens(320, n, 3 + i) for i, n in enumerate([9, 40, 1])]
+    ref = None
+    for freq in (1, 4, 10):
+        fg = Fastgen.build(HfLoader(model_dir), GenArgs(use_sampling=True, temperature=0.8, top_p=0.9, max_gen=30,
+                                                        cache_block=16, max_seq=512, seed=5, max_batch=4,
+                                                        sync_freq=freq), device="cuda:0", dtype=torch.float32)
+        if ref is not None:
+            fg.scheduler.stop_tokens = {ref[0][13]}  # falls inside a run of the first request
+        q = queue.Queue()
+        for i, p in enumerate(prompts):
+            q.put(Packet(thread_id=i, tokens=p))
+        q.put(None)
+        out = {pkt.thread_id: pkt.tokens for pkt in fg.generate(q)}
+        fg.destroy()
+        if ref is None:
+            ref = out
+            continue
+        stop = ref[0][13]
+        for i in range(len(prompts)):
+            want = ref[i][: ref[i].index(stop) + 1] if stop in ref[i] else ref[i]
+            assert out[i] == want, f"sync_freq {freq}, request {i}"
+
+
 def test_stop_token_and_errors(tmp_path):
     model_dir = H.make_model_dir(tmp_path, "tiny_a")
     model = pl.read_model(model_dir)
