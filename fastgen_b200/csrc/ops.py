@@ -143,7 +143,15 @@ def require_cuda(device) -> torch.device:
     return device
 
 
+_device_index = 0  # set by Ops: the engine runs on one device
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Asked for at every launch, so through torch's
+    direct call where it has one (the public way costs several microseconds)."""
+    if _raw_stream is not None:
+        return _raw_stream(_device_index)
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -166,6 +174,8 @@ class Ops:
 
     def __init__(self, dtype: torch.dtype, device) -> None:
         self.device = require_cuda(device)
+        global _device_index
+        _device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.act_dtype = dtype
         self.code = _code(dtype)
         self.lib = core()

@@ -78,6 +78,8 @@ class DecodeGraphs:
         self.sizes = bucket_sizes(max_batch, num_graphs)
         self.buckets: Dict[tuple, _Bucket] = {}
         self.pool = None
+        self.capture_stream = None
+        self.warmed = set()  # batch sizes that ran once outside a capture
         self.replays = 0
         self.last_h2d_bytes = 0
 
@@ -117,18 +119,32 @@ class DecodeGraphs:
         model, memories = self.model, self.memories
         if b.graph is None:
             ctx = b.context(self.device)
-            # once eagerly (libraries load, attributes get set), then capture
-            model.forward(ctx, memories)
-            torch.cuda.synchronize()
+            if size not in self.warmed:
+                # once eagerly for a batch size (libraries load and choose their kernels,
+                # function attributes get set), then capture
+                model.forward(ctx, memories)
+                self.warmed.add(size)
             graph = torch.cuda.CUDAGraph()
             before = Ops.launches
-            # the collector stays off while capturing: destroying an old graph or
-            # freeing device memory in the middle of a capture would invalidate it
+            # Captured by hand on a stream of its own: torch.cuda.graph() would also run the
+            # collector and empty the allocator's cache, tens of milliseconds a capture, and
+            # captures happen while requests are being served.  The collector stays off while
+            # capturing: destroying an old graph or freeing device memory in the middle of a
+            # capture would invalidate it.
+            if self.capture_stream is None:
+                self.capture_stream = torch.cuda.Stream(self.device)
             gc_was_on = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph, pool=self.pool):
-                    b.logits = model.forward(ctx, memories)
+                self.capture_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.capture_stream):
+                    kw = {} if self.pool is None else {"pool": self.pool}
+                    graph.capture_begin(**kw)
+                    try:
+                        b.logits = model.forward(ctx, memories)
+                    finally:
+                        graph.capture_end()
+                torch.cuda.current_stream().wait_stream(self.capture_stream)
             finally:
                 if gc_was_on:
                     gc.enable()

@@ -29,9 +29,9 @@ from typing import Any, Deque, List, Optional, Sequence
 from ..cache import CacheManager, OutOfPages
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
-    """A request in flight."""
+    """A request in flight (compared and hashed by identity)."""
 
     thread_id: Any
     prompt: List[int]
@@ -47,6 +47,15 @@ class Request:
 
     def all_tokens(self) -> List[int]:
         return self.prompt + self.generated
+
+    def tokens_between(self, a: int, b: int) -> List[int]:
+        """Tokens ``a .. b-1`` of prompt + generated, without joining the two lists."""
+        n = len(self.prompt)
+        if b <= n:
+            return self.prompt[a:b]
+        if a >= n:
+            return self.generated[a - n : b - n]
+        return self.prompt[a:] + self.generated[: b - n]
 
     def __len__(self) -> int:
         return len(self.prompt) + len(self.generated)
@@ -141,8 +150,9 @@ class Scheduler:
         entries: List[PlanEntry] = []
         budget = self.token_budget
         order = sorted(self.running, key=lambda r: (len(r) - r.fed != 1,))  # stable: decoders first
+        preempted = set()
         for req in order:
-            if req not in self.running:
+            if req in preempted:
                 continue  # preempted while planning
             if budget == 0:
                 break
@@ -160,12 +170,13 @@ class Scheduler:
                         entries.remove(e)
                         budget += len(e.tokens)
                     self._preempt(victim)
+                    preempted.add(victim)
                     if victim is req:
                         n = 0
                         break
             if n == 0:
                 continue
-            toks = req.all_tokens()[req.fed : req.fed + n]
+            toks = req.tokens_between(req.fed, req.fed + n)
             entries.append(PlanEntry(req, toks, samples=(req.fed + n == len(req))))
             budget -= n
         return entries
