@@ -126,6 +126,10 @@ class RequestCache:
         self.slot = slot
         self.length = 0  # tokens whose keys/values (or state) are in the cache
         self.pages: List[Dict[int, int]] = [dict() for _ in range(n_groups)]  # logical -> page
+        # Positions below this have a page in every group.  A request's pages in a group are
+        # a contiguous run of logical pages (taken upward, given back from below), so the
+        # bound answers most reservations of a decoding request without a look at the maps.
+        self.reserved = 0
 
     def n_pages(self) -> int:
         return sum(len(p) for p in self.pages)
@@ -245,6 +249,8 @@ class CacheManager:
 
     def pages_needed(self, req: RequestCache, new_length: int) -> List[int]:
         """New pages per group that ``req`` needs to hold ``new_length`` tokens."""
+        if new_length <= req.reserved:
+            return [0] * len(self.groups)
         out = []
         for gi, grp in enumerate(self.groups):
             have = req.pages[gi]
@@ -287,6 +293,8 @@ class CacheManager:
                 f"request {req.request_id!r} would hold {new_length} tokens; the cache "
                 f"was built for at most {self.max_length} per request"
             )
+        if new_length <= req.reserved:
+            return
         need = self.pages_needed(req, new_length)
         for n, grp in zip(need, self.groups):
             if n > grp.pool.n_free:
@@ -302,6 +310,9 @@ class CacheManager:
                 req.pages[gi][lp] = page
                 grp.host_table[req.slot, lp] = page
                 grp.dirty.append((req.slot, lp, page))
+        if self.groups:
+            req.reserved = min((max(req.pages[gi]) + 1) * grp.page_size if req.pages[gi] else 0
+                               for gi, grp in enumerate(self.groups))
 
     def advance(self, req: RequestCache, new_length: int) -> None:
         """Record that ``req`` now holds ``new_length`` tokens and give back the
@@ -384,6 +395,11 @@ class CacheManager:
                     seen[page] = req.request_id
                     if grp.host_table[req.slot, lp] != page:
                         raise CacheError("block table disagrees with a request's pages")
+                held = req.pages[gi]
+                if held and sorted(held) != list(range(min(held), max(held) + 1)):
+                    raise CacheError(f"request {req.request_id!r} holds a broken run of pages in group {gi}")
+                if req.reserved > ((max(held) + 1) * grp.page_size if held else 0):
+                    raise CacheError(f"request {req.request_id!r}: reserved bound beyond its pages in group {gi}")
             if len(seen) + grp.pool.n_free != grp.pool.n_pages:
                 raise CacheError(
                     f"group {gi}: {len(seen)} held + {grp.pool.n_free} free != {grp.pool.n_pages}"

@@ -198,15 +198,18 @@ class Scheduler:
                 n = min(n, req.max_gen - len(req.generated))
         if n <= 1:
             return 1
+        free = self.cache.free_pages()
+        total = [0] * len(free)
+        handles = []
         for req in self.running:
-            if any(need > free for need, free in zip(
-                    self.cache.pages_needed(self.cache.get(id(req)), req.fed + n), self.cache.free_pages())):
-                return 1
-        try:
-            for req in self.running:
-                self.cache.reserve(self.cache.get(id(req)), req.fed + n)
-        except OutOfPages:
-            return 1  # what was reserved stays with its request; the one-step path decides
+            handle = self.cache.get(id(req))
+            handles.append(handle)
+            for gi, need in enumerate(self.cache.pages_needed(handle, req.fed + n)):
+                total[gi] += need
+        if any(t > f for t, f in zip(total, free)):
+            return 1  # not enough pages for the whole run: the one-step path decides (and preempts)
+        for req, handle in zip(self.running, handles):
+            self.cache.reserve(handle, req.fed + n)
         return n
 
     def commit_decode_run(self, requests: Sequence[Request], sampled: Sequence[Sequence[int]],
