@@ -41,6 +41,7 @@ CORE_SOURCES = [
     "silu_gate.cu",
     "gemm_f32.cu",
     "gemm_skinny.cu",
+    "gemm_stream.cu",
     "sampling.cu",
     "tensor_map.cu",
 ]

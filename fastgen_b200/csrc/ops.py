@@ -50,6 +50,7 @@ _CORE_SIGNATURES = {
     "fg_gemm_skinny_swiglu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "fg_gemm_skinny_qkv_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                                 _P, _P],
+    "fg_gemm_stream_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _I, _P, _P],
     "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
     "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
     "fg_make_kv_tensor_map": [_P, _P, _I, _I, _I, _I, _I, _I],
@@ -181,6 +182,8 @@ class Ops:
         self.lib = core()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch = {}
+        self._stream_scratch = None
+        self._stream_counters = None
         self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
         # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
@@ -267,6 +270,30 @@ class Ops:
             out.copy_(res)
             return out
         return res
+
+    def linear_stream(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                      out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``x @ w.T`` for up to 256 tokens with this package's tcgen05 weight-streaming
+        product (bfloat16 operands; the work is cut evenly over the SMs)."""
+        m, k = x.shape
+        n = w.shape[0]
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
+        assert x.stride(1) == 1 and w.stride(1) == 1
+        if out is None:
+            out = torch.empty((m, n), dtype=out_dtype or torch.bfloat16, device=x.device)
+        assert out.stride(1) == 1
+        if self._stream_scratch is None:
+            lib = self.lib
+            lib.fg_gemm_stream_scratch_floats.restype = ctypes.c_longlong
+            floats = lib.fg_gemm_stream_scratch_floats(lib.fg_gemm_stream_max_m())
+            self._stream_scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
+            # arrival counts: zero before the first call, left at zero by every call
+            self._stream_counters = torch.zeros(8192, dtype=torch.int32, device=self.device)
+        _check(self.lib, self.lib.fg_gemm_stream_bf16(
+            _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out.dtype), m, n, k,
+            _ptr(self._stream_scratch), self._stream_scratch.numel(), _ptr(self._stream_counters),
+            self._stream_counters.numel(), _ptr(self.status), _stream()))
+        return out
 
     def _skinny_ok(self, x: torch.Tensor, w: torch.Tensor, k: int) -> bool:
         return (x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_M and k % 8 == 0
