@@ -39,7 +39,7 @@ constexpr int TILE_N = 128;   // rows of W a tile (the M side of the instruction
 constexpr int CHUNK_K = 64;   // k elements a stage: 128 bytes a row, the swizzle span
 constexpr int GS_THREADS = 192;  // TMA warp, MMA warp, four epilogue warps
 constexpr int W_STAGE = TILE_N * 128;
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 12;
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
@@ -96,7 +96,7 @@ struct Segments {
 };
 
 template <typename TO>
-__global__ void __launch_bounds__(GS_THREADS, 1)
+__global__ void __launch_bounds__(GS_THREADS, 2)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                    TO* __restrict__ y, int ldy, int M, int N, int m_pad, int n_stages, Cut cut, float* partials,
                    int* arrivals, int tmem_cols, int* status) {
@@ -132,7 +132,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 
   if (warp == 0) {
     // ================================ TMA warp ================================
-    if (lane == 0) {
+    // The copies of consecutive stages are issued by different lanes (the lanes walk the
+    // same list; lane it % ISSUERS issues stage it).
+    {
+      constexpr int ISSUERS = 4;
       // The weights do not depend on the kernel before this one: the first stages' W tiles
       // are on their way while that kernel finishes; x (its output) is touched after the wait.
       Segments pre(cut, blockIdx.x);
@@ -143,17 +146,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       while (it < n_pre && pre.next(tile, c0, c1))
         for (int c = c0; c < c1 && it < n_pre; ++c, ++it) {
           pre_chunk[it] = c;
-          mbar_arrive_expect(&full[it], stage_bytes);
-          tma_load_2d(smem + it * stage_bytes, &w_map, c * CHUNK_K, tile * TILE_N, &full[it]);
+          if (lane == it % ISSUERS) {
+            mbar_arrive_expect(&full[it], stage_bytes);
+            tma_load_2d(smem + it * stage_bytes, &w_map, c * CHUNK_K, tile * TILE_N, &full[it]);
+          }
         }
       pdl_wait();
       for (int i = 0; i < n_pre; ++i)
-        tma_load_2d(smem + i * stage_bytes + W_STAGE, &x_map, pre_chunk[i] * CHUNK_K, 0, &full[i]);
+        if (lane == i % ISSUERS)
+          tma_load_2d(smem + i * stage_bytes + W_STAGE, &x_map, pre_chunk[i] * CHUNK_K, 0, &full[i]);
       Segments seg(cut, blockIdx.x);
       it = 0;
       while (seg.next(tile, c0, c1))
         for (int c = c0; c < c1; ++c, ++it) {
-          if (it < n_pre) continue;
+          if (it < n_pre || lane != it % ISSUERS) continue;
           const int s = it % n_stages;
           mbar_wait(&empty[s], (it / n_stages - 1) & 1, status);
           mbar_arrive_expect(&full[s], stage_bytes);
@@ -162,27 +168,35 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           tma_load_2d(dst + W_STAGE, &x_map, c * CHUNK_K, 0, &full[s]);
         }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ================================ MMA warp ================================
     if (lane == 0) {
       const uint64_t desc0 = smem_desc(smem, 16);
       Segments seg(cut, blockIdx.x);
-      int tile, c0, c1, it = 0, n_seg = 0;
+      int tile, c0, c1, n_seg = 0;
+      int s = 0, parity = 0;  // the stage in turn and the parity of its fill
+      const uint64_t stage_desc = (uint64_t)(stage_bytes >> 4);
+      uint64_t wd = desc0;
       while (seg.next(tile, c0, c1)) {
         const int buf = n_seg & 1;
         if (n_seg >= 2) mbar_wait(&acc_empty[buf], ((n_seg >> 1) - 1) & 1, status);
         tc_fence_after();
-        for (int c = c0; c < c1; ++c, ++it) {
-          const int s = it % n_stages;
-          mbar_wait(&full[s], (it / n_stages) & 1, status);
+        const uint32_t d_tmem = tmem + buf * m_pad;
+        for (int c = c0; c < c1; ++c) {
+          mbar_wait(&full[s], parity, status);
           tc_fence_after();
-          const uint64_t wd = desc0 + (uint64_t)((s * stage_bytes) >> 4);
           const uint64_t xd = wd + (uint64_t)(W_STAGE >> 4);
 #pragma unroll
           for (int kk = 0; kk < CHUNK_K / 16; ++kk)
-            umma_f16(tmem + buf * m_pad, wd + (uint64_t)(kk * 2), xd + (uint64_t)(kk * 2), idesc,
-                     (c > c0 || kk > 0) ? 1u : 0u);
+            umma_f16(d_tmem, wd + (uint64_t)(kk * 2), xd + (uint64_t)(kk * 2), idesc, (c > c0 || kk > 0) ? 1u : 0u);
           umma_commit(&empty[s]);  // the stage is free once these products have read it
+          wd += stage_desc;
+          if (++s == n_stages) {
+            s = 0;
+            parity ^= 1;
+            wd = desc0;
+          }
         }
         umma_commit(&acc_full[buf]);
         ++n_seg;
@@ -318,7 +332,7 @@ extern "C" int fg_gemm_stream_max_m() { return 256; }
 // at zero by every call) that a product with these sizes needs.
 extern "C" long long fg_gemm_stream_scratch_floats(int M) {
   const int m_pad = (M + 15) / 16 * 16;
-  return (long long)sm_count() * m_pad * TILE_N;
+  return (long long)2 * sm_count() * m_pad * TILE_N;  // a partial a block, up to two blocks an SM
 }
 extern "C" int fg_gemm_stream_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
 
@@ -341,9 +355,13 @@ extern "C" int fg_gemm_stream_bf16(const void* x, int ldx, const void* w, int ld
   Cut cut;
   cut.total = (long long)n_tiles * n_chunks;
   cut.n_chunks = n_chunks;
-  cut.grid = (int)(cut.total < sm_count() ? cut.total : sm_count());
+  // Two blocks an SM where the ring allows it: one block's single TMA-issuing and
+  // MMA-issuing threads sustain about 30 GB/s, less than an SM's share of the HBM stream.
   const int stage_bytes = W_STAGE + m_pad * 128;
-  int n_stages = (220 * 1024) / stage_bytes;
+  const int per_sm = 110 * 1024 / stage_bytes >= 3 ? 2 : 1;
+  const int blocks = per_sm * sm_count();
+  cut.grid = (int)(cut.total < blocks ? cut.total : blocks);
+  int n_stages = ((per_sm == 2 ? 110 : 220) * 1024) / stage_bytes;
   if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
   FG_CHECK_ARG(n_stages >= 2, "fg_gemm_stream_bf16: no room for two stages at M=%d", M);
   int tmem_cols = 32;

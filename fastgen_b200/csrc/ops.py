@@ -185,6 +185,9 @@ class Ops:
         self._stream_scratch = None
         self._stream_counters = None
         self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
+        # FG_STREAM_GEMM: "off" never uses the tcgen05 weight-streaming product, "all" uses it
+        # for every product of 9..256 tokens, default: where it measured faster than the library
+        self.stream_gemm = os.environ.get("FG_STREAM_GEMM", "auto")
         # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -262,6 +265,10 @@ class Ops:
                 _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out.dtype),
                 m, n, k, _stream()))
             return out
+        if self._stream_ok(m, n, k, x, w):
+            # a decode batch against a very tall matrix (the vocabulary): this package's tcgen05
+            # weight-streaming product; elsewhere the library's is as fast or faster
+            return self.linear_stream(x, w, out=out, out_dtype=want)
         if want == torch.bfloat16:
             return torch.mm(x, w.t(), out=out) if out is not None else torch.mm(x, w.t())
         # float32 result of a bfloat16 product (logits)
@@ -270,6 +277,15 @@ class Ops:
             out.copy_(res)
             return out
         return res
+
+    def _stream_ok(self, m: int, n: int, k: int, x: torch.Tensor, w: torch.Tensor) -> bool:
+        if self.stream_gemm == "off":
+            return False
+        fits = (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1
+                and w.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+        if self.stream_gemm == "all":
+            return fits and SKINNY_MAX_M < m <= 256
+        return fits and 48 <= m <= 96 and n * k >= (1 << 28)
 
     def linear_stream(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:

@@ -252,6 +252,27 @@ def test_rope_kv_write(ops32, dtype, hq, hkv, hd, page):
         ops32.check_status()
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 128, 64), (9, 4096, 4096), (33, 1000, 200), (64, 6144, 4096),
+                                   (100, 28672, 4096), (64, 4096, 14336), (128, 331, 72), (256, 2048, 512)])
+def test_linear_stream(ops16, m, n, k):
+    """The tcgen05 weight-streaming product: tiles that fall to one block, tiles split over
+    several blocks (partial sums through scratch), sizes that are no multiple of the tile."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(DEV, torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        y = ops16.linear_stream(x, w, out_dtype=out_dtype)
+        ops16.check_status()
+        tol = float(ref.abs().max()) * (2.0 ** -7 if out_dtype == torch.bfloat16 else 1e-5) + 1e-3
+        assert float((y.double() - ref).abs().max()) <= tol
+    again = ops16.linear_stream(x, w, out_dtype=torch.float32)  # the arrival counts are back at zero
+    assert torch.equal(again, y)
+    # a token's result does not depend on the batch it is in
+    alone = ops16.linear_stream(x[:9].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(alone, y[:9])
+
+
 # ---------------------------------------------------------------------------------
 # attention: a step context by hand, a paged cache with shuffled pages
 # ---------------------------------------------------------------------------------
