@@ -207,7 +207,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const size_t psmem = decode_persistent_smem_bytes<FG_HEAD_DIM>(group);
-  if (items >= 4 * n_sms && group <= PS_MAX_GROUP && psmem <= 227 * 1024 - 256) {
+  if (items >= 4 * n_sms && group <= PS_MAX_GROUP && n_seqs <= PS_MAX_SEQS && psmem <= 227 * 1024 - 4352 - 256) {
     auto pkern = attention_decode_persistent_kernel<FG_HEAD_DIM>;
     static size_t pattr_set = 0;
     if (pattr_set < psmem) {

@@ -268,6 +268,7 @@ constexpr int PS_THREADS = 160;  // 4 consumer warps + 1 producer warp
 constexpr int PS_CONSUMERS = 128;
 constexpr int PS_SLOTS = 3;
 constexpr int PS_MAX_GROUP = 8;
+constexpr int PS_MAX_SEQS = 512;   // requests whose positions a block keeps in shared memory
 
 template <int HD>
 __host__ __device__ constexpr int ps_merge_ld() { return HD + 4; }  // rows of the merge buffer fall on different banks
@@ -306,6 +307,9 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
   float* wm = wo + 4 * group * MLD;                                        // [4][8] maxima
   float* wl = wm + 4 * PS_MAX_GROUP;                                       // [4][8] sums
   __shared__ __align__(8) uint64_t full[PS_SLOTS], empty[PS_SLOTS];
+  // per request: the token's position (-1: padding lane) and the number of (request, split)
+  // pairs before it
+  __shared__ int s_pos[PS_MAX_SEQS], s_cum[PS_MAX_SEQS + 1];
 
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -316,6 +320,36 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     mbar_fence_init();
   }
+  // Requests differ in length, and a request only has the splits its keys reach: the items
+  // are the (request, split, kv head) triples that exist, numbered request by request, so
+  // that block b takes items b, b + G, ... and every block gets the same number of them.
+  // Positions are inputs of the step (no kernel of the step writes them).
+  auto first_split = [&](int p) { return window > 0 ? max(0, p - window + 1) / SPLIT : 0; };
+  for (int sq = tid; sq < n_seqs; sq += PS_THREADS) s_pos[sq] = seq_req[sq] < 0 ? -1 : pos[seq_tok[sq]];
+  __syncthreads();
+  if (warp == 0) {
+    // an exclusive scan of the split counts: each lane sums a stretch, the warp scans the sums
+    const int per_lane = (n_seqs + 31) / 32;
+    const int lo = lane * per_lane, hi = min(n_seqs, lo + per_lane);
+    int sum = 0;
+    for (int sq = lo; sq < hi; ++sq) {
+      const int p = s_pos[sq];
+      sum += p < 0 ? 0 : min(p / SPLIT, max_splits - 1) - first_split(p) + 1;
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;
+    for (int sq = lo; sq < hi; ++sq) {
+      s_cum[sq] = run;
+      const int p = s_pos[sq];
+      run += p < 0 ? 0 : min(p / SPLIT, max_splits - 1) - first_split(p) + 1;
+    }
+    if (lane == 31) s_cum[n_seqs] = incl;
+  }
   __syncthreads();
   // The step's own kernels write keys and values at the tokens' positions only: the
   // producer loads splits that end before the token's position without waiting for the
@@ -324,20 +358,21 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
 
   const int box_rows = min(page_size, SPLIT);
   const int n_boxes = SPLIT / box_rows;
-  const int total = n_seqs * n_kv_heads * max_splits;
-  // Both kinds of warps walk the same list and skip the same items (padding lanes,
-  // splits beyond the request's keys or before its window).
+  const int total = s_cum[n_seqs] * n_kv_heads;
+  // Both kinds of warps walk the same list.
   auto item_of = [&](int item, int& seq, int& g, int& split, int& p, int& k_begin) -> bool {
-    split = item % max_splits;
-    const int rest = item / max_splits;
-    g = rest % n_kv_heads;
-    seq = rest / n_kv_heads;
-    if (seq_req[seq] < 0) return false;
-    p = pos[seq_tok[seq]];
-    const int k0 = split * SPLIT;
-    if (k0 > p) return false;
+    g = item % n_kv_heads;
+    const int r = item / n_kv_heads;
+    int lo = 0, hi = n_seqs;  // the last request whose first pair is <= r
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_cum[mid] <= r) lo = mid; else hi = mid;
+    }
+    seq = lo;
+    p = s_pos[seq];
+    split = first_split(p) + (r - s_cum[seq]);
     k_begin = window > 0 ? max(0, p - window + 1) : 0;
-    return k0 + SPLIT > k_begin;
+    return true;
   };
 
   if (warp == 4) {
