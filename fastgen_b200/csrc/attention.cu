@@ -215,7 +215,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
       FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
       pattr_set = psmem;
     }
-    fg_launch_pdl(pkern, dim3(2 * n_sms), dim3(PS_THREADS), psmem, stream, km, vm, layer, (const __nv_bfloat16*)q,
+    fg_launch_pdl(pkern, dim3(ps_blocks_per_sm<FG_HEAD_DIM>() * n_sms), dim3(PS_THREADS), psmem, stream, km, vm, layer, (const __nv_bfloat16*)q,
                   q_stride, block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_seqs, n_heads,
                   n_kv_heads, group, window, scale * 1.4426950408889634f, scratch, max_splits, status);
   } else {

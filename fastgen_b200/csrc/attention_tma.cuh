@@ -286,8 +286,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
+// blocks an SM: the ring of a head size of 64 is half as large, and its items are half as
+// long for the same work around them, so a third block pays
 template <int HD>
-__global__ void __launch_bounds__(PS_THREADS, 2)
+constexpr int ps_blocks_per_sm() { return HD <= 64 ? 3 : 2; }
+
+template <int HD>
+__global__ void __launch_bounds__(PS_THREADS, ps_blocks_per_sm<HD>())
 attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
                                    const __grid_constant__ CUtensorMap v_map, int layer,
                                    const __nv_bfloat16* q, int q_stride,
