@@ -21,16 +21,17 @@ __global__ void silu_gate_kernel(const T* __restrict__ x, T* __restrict__ out, i
   }
 }
 
-// bfloat16 rows whose width is a multiple of 8: eight elements (16 bytes) a thread
-__global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
-                                        int ffn, size_t total8, int interleave) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  const int per_row = ffn / 8;
-  for (; i < total8; i += stride) {
-    const size_t t = i / per_row, f = (i - t * per_row) * 8;
-    const uint4 g4 = *reinterpret_cast<const uint4*>(x + t * 2 * ffn + (interleave ? 2 * f : f));
-    const uint4 u4 = *reinterpret_cast<const uint4*>(x + t * 2 * ffn + (interleave ? 2 * f + 8 : ffn + f));
+// bfloat16 rows whose width is a multiple of 8: eight elements (16 bytes) a thread.
+// blockIdx.x walks a row's 16-byte pieces, blockIdx.y (and a stride loop) the rows, so no
+// index needs a division; two rows are in flight a thread.
+__global__ void __launch_bounds__(256)
+silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int ffn, int n_rows,
+                        int interleave) {
+  const int piece = blockIdx.x * blockDim.x + threadIdx.x;
+  if (piece >= ffn / 8) return;
+  const int f = piece * 8;
+  const int g_off = interleave ? 2 * f : f, u_off = interleave ? 2 * f + 8 : ffn + f;
+  auto gate = [](uint4 g4, uint4 u4) {
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
     uint4 o4;
@@ -40,7 +41,21 @@ __global__ void silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __n
       const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
       o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
     }
-    *reinterpret_cast<uint4*>(out + t * ffn + f) = o4;
+    return o4;
+  };
+  int t = blockIdx.y;
+  for (; t + (int)gridDim.y < n_rows; t += 2 * gridDim.y) {
+    const __nv_bfloat16* r0 = x + (size_t)t * 2 * ffn;
+    const __nv_bfloat16* r1 = x + (size_t)(t + gridDim.y) * 2 * ffn;
+    const uint4 g0 = *reinterpret_cast<const uint4*>(r0 + g_off), u0 = *reinterpret_cast<const uint4*>(r0 + u_off);
+    const uint4 g1 = *reinterpret_cast<const uint4*>(r1 + g_off), u1 = *reinterpret_cast<const uint4*>(r1 + u_off);
+    *reinterpret_cast<uint4*>(out + (size_t)t * ffn + f) = gate(g0, u0);
+    *reinterpret_cast<uint4*>(out + (size_t)(t + gridDim.y) * ffn + f) = gate(g1, u1);
+  }
+  if (t < n_rows) {
+    const __nv_bfloat16* r0 = x + (size_t)t * 2 * ffn;
+    *reinterpret_cast<uint4*>(out + (size_t)t * ffn + f) =
+        gate(*reinterpret_cast<const uint4*>(r0 + g_off), *reinterpret_cast<const uint4*>(r0 + u_off));
   }
 }
 
@@ -54,11 +69,11 @@ extern "C" int fg_silu_gate(const void* x, void* out, int dtype, int n_rows, int
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == FG_BF16 && ffn % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
-    const size_t total8 = total / 8;
-    size_t b8 = (total8 + threads - 1) / threads;
-    if (b8 > 148 * 16) b8 = 148 * 16;
-    silu_gate_bf16x8_kernel<<<(int)b8, threads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, ffn,
-                                                             total8, interleave);
+    const int bx = (ffn / 8 + threads - 1) / threads;
+    int by = n_rows < 65535 ? n_rows : 65535;
+    while (by > 1 && (long long)bx * by > 148 * 32) by = (by + 1) / 2;  // rows beyond the grid: the stride loop
+    silu_gate_bf16x8_kernel<<<dim3(bx, by), threads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, ffn,
+                                                                  n_rows, interleave);
   } else if (dtype == FG_F32)
     silu_gate_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)x, (float*)out, ffn, total, interleave);
   else if (dtype == FG_BF16)
