@@ -140,6 +140,37 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
   // The weights do not depend on the kernel before this one: their first stages are on
   // their way while that kernel finishes.  x (its output) is only touched after the wait.
   pdl_trigger();
+  // QKV epilogue: what depends on the token's position alone (angle, page) is worked out
+  // now, while the weights stream, so that the end of the block is a rotation and a store.
+  // Positions, requests and block tables are inputs of the step.
+  int e_tok = -1, e_n = 0, e_kind = 0;  // kind 0: query, 1: key, 2: value; e_tok < 0: nothing to write
+  float e_sin = 0.f, e_cos = 1.f;
+  size_t e_dst = 0;
+  if (EPI == EPI_QKV && tid < (ROWS / 2) * NT * 8) {
+    const int hd = qkv.head_dim, q_width = qkv.n_heads * hd, kv_width = qkv.n_kv_heads * hd;
+    const int tok = tid / (ROWS / 2), pr = tid - tok * (ROWS / 2);
+    const int n = n0 + 2 * pr;
+    const int slot_req = tok < M ? qkv.req[tok] : -1;
+    if (n < N && slot_req >= 0) {
+      const int p = qkv.pos[tok];
+      e_kind = n < q_width ? 0 : (n < q_width + kv_width ? 1 : 2);
+      if (e_kind != 2 && qkv.freqs != nullptr) sincosf((float)p * qkv.freqs[(n % hd) >> 1], &e_sin, &e_cos);
+      e_tok = tok;
+      e_n = n;
+      if (e_kind != 0) {
+        const int col = n - q_width - (e_kind == 2 ? kv_width : 0);
+        const int g = col / hd, d = col - g * hd;
+        const int logical = p / qkv.page_size;
+        const int page = logical < qkv.table_width ? qkv.block_table[(size_t)slot_req * qkv.table_width + logical] : -1;
+        if (page < 0 || page >= qkv.n_pages) {
+          if (qkv.status) atomicOr(qkv.status, FG_STATUS_BAD_PAGE);
+          e_tok = -1;
+        } else {
+          e_dst = (((size_t)page * qkv.n_kv_heads + g) * qkv.page_size + (p - logical * qkv.page_size)) * hd + d;
+        }
+      }
+    }
+  }
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s)
     if (s < my_chunks) issue(s, true, false);
@@ -196,43 +227,24 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
       }
     }
   } else {
-    // the block's 16 rows are 8 adjacent pairs of one head of q, k or v
-    const int hd = qkv.head_dim, q_width = qkv.n_heads * hd, kv_width = qkv.n_kv_heads * hd;
-    for (int i = tid; i < (ROWS / 2) * NT * 8; i += THREADS) {
-      const int tok = i / (ROWS / 2), pr = i - tok * (ROWS / 2);
-      const int n = n0 + 2 * pr;
-      if (tok >= M || n >= N) continue;
-      const int slot_req = qkv.req[tok];
-      if (slot_req < 0) continue;  // padding lane
-      float re = total(2 * pr, tok), im = total(2 * pr + 1, tok);
-      const int p = qkv.pos[tok];
-      const bool is_v = n >= q_width + kv_width;
-      if (!is_v) {
+    // the block's 16 rows are 8 adjacent pairs of one head of q, k or v; a thread's pair,
+    // angle and destination were worked out before the main loop
+    if (e_tok >= 0) {
+      const int pr = (e_n - n0) >> 1;
+      float re = total(2 * pr, e_tok), im = total(2 * pr + 1, e_tok);
+      if (e_kind != 2) {
         // the product is rounded to bfloat16 before the rotation, as a separate kernel would see it
         re = __bfloat162float(__float2bfloat16_rn(re));
         im = __bfloat162float(__float2bfloat16_rn(im));
-        float s = 0.f, cs = 1.f;
-        if (qkv.freqs != nullptr) sincosf((float)p * qkv.freqs[(n % hd) >> 1], &s, &cs);
-        const float rr = re * cs - im * s, ii = im * cs + re * s;
+        const float rr = re * e_cos - im * e_sin, ii = im * e_cos + re * e_sin;
         re = rr;
         im = ii;
       }
       const __nv_bfloat162 out2 = __floats2bfloat162_rn(re, im);
-      if (n < q_width) {
-        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(y) + (size_t)tok * ldy + n) = out2;
-        continue;
-      }
-      const int col = n - q_width - (is_v ? kv_width : 0);
-      const int g = col / hd, d = col - g * hd;
-      const int logical = p / qkv.page_size;
-      const int page = logical < qkv.table_width ? qkv.block_table[(size_t)slot_req * qkv.table_width + logical] : -1;
-      if (page < 0 || page >= qkv.n_pages) {
-        if (qkv.status) atomicOr(qkv.status, FG_STATUS_BAD_PAGE);
-        continue;
-      }
-      const size_t dst =
-          (((size_t)page * qkv.n_kv_heads + g) * qkv.page_size + (p - logical * qkv.page_size)) * hd + d;
-      *reinterpret_cast<__nv_bfloat162*>((is_v ? qkv.v_pages : qkv.k_pages) + dst) = out2;
+      if (e_kind == 0)
+        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(y) + (size_t)e_tok * ldy + e_n) = out2;
+      else
+        *reinterpret_cast<__nv_bfloat162*>((e_kind == 2 ? qkv.v_pages : qkv.k_pages) + e_dst) = out2;
     }
   }
 }
