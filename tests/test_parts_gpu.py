@@ -276,6 +276,40 @@ def test_first_tokens(tmp_path, dtype):
     H.compare(model_dir, reqs, H.collect(steps, outputs), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_prompt_in_large_portions(tmp_path, dtype):
+    """A prompt of thousands of tokens in portions of thousands (dozens of key tiles a query
+    tile, llama3-scaled angles beyond the original context), then single tokens over dozens
+    of key splits."""
+    cfg = dict(
+        architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_size=344, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, vocab_size=300, tie_word_embeddings=False,
+        rope_theta=500000.0,
+        rope_scaling=dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=1024),
+        max_position_embeddings=16384,
+    )
+    from fastgen_b200.weights import write_random_model
+    model_dir = write_random_model(tmp_path / "long", cfg, seed=3, norm_jitter=0.1)
+    n = 6200
+    toks = H.random_tokens(300, n, 1)
+    head = n - 6
+    steps, p = [], 0
+    for chunk in (3000, 2048, head - 5048):
+        steps.append(dict(step=len(steps), entries=[dict(id="a", tokens=toks[p:p + chunk], want=[0, chunk // 2, chunk - 1])],
+                          end=[]))
+        p += chunk
+    for p in range(head, n):
+        steps.append(dict(step=len(steps), entries=[dict(id="a", tokens=[toks[p]], want=[0])], end=[]))
+    outputs, _ = H.run_engine(model_dir, dtype, steps, page_size=64, max_tokens=8192)
+    got = H.collect(steps, outputs)["a"]
+    ref = H.plain_logits(model_dir, toks)
+    assert len(got) == 9 + 6
+    for p, row in got.items():
+        err = float(np.abs(row - ref[p]).max())
+        tol = 1e-4 if dtype == torch.float32 else 0.02 * max(1.0, float(np.abs(ref[p]).max()))
+        assert err <= tol, (p, err)
+
+
 def test_many_key_splits_through_graphs(tmp_path):
     """Four live requests with thousands of cached keys and eight key/value heads: enough
     (request, head, split) items for the persistent single-token kernel, inside captured
