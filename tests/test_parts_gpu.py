@@ -14,8 +14,9 @@ import helpers as H
 import plain_llama as pl
 from fastgen_b200.config import LayerSpec, ModelArgs, PartSpec, ScheduleEntry, register_architecture
 from fastgen_b200.parts import (
-    AttentionParams, CacheSpec, Llama3Scaling, Mixer, NoPositionParams, RMSNormParams, RopeParams, StateSpec,
-    SwiGLUParams, WeightSpec, make_feed_forward, make_mixer, make_norm, make_position, register_mixer,
+    AttentionParams, Block, CacheSpec, FeedForward, Llama3Scaling, Mixer, NoPositionParams, Norm, PositionEncoding,
+    RMSNormParams, RopeParams, StateSpec, SwiGLUParams, WeightSpec, make_feed_forward, make_mixer, make_norm,
+    make_position, register_block, register_feed_forward, register_mixer, register_norm, register_position,
 )
 
 pytestmark = pytest.mark.gpu
@@ -232,6 +233,153 @@ def test_toy_architecture_with_stateful_mixer(tmp_path, dtype):
     got = H.collect(steps, outputs)
     for rid, toks in reqs.items():
         ref = _toy_plain(w, toks).numpy()
+        for p, row in got[rid].items():
+            err = np.abs(row - ref[p]).max()
+            tol = 1e-4 if dtype == torch.float32 else 0.02 * max(1.0, np.abs(ref[p]).max())
+            assert err <= tol, (rid, p, err)
+
+
+# ---------------------------------------------------------------------------------
+# a second toy architecture: a feed-forward with routing, a position encoding of its own,
+# a norm of its own and another arrangement of the block, all registered from here
+# ---------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RoutedParams:
+    dim: int
+    ffn_dim: int
+    n_experts: int
+
+
+class RoutedFeedForward(FeedForward):
+    """y = sum_e softmax(x R^T)_e * W2_e relu(W1_e x): router logits and weights in float32."""
+
+    def weight_specs(self):
+        p = self.params
+        return [WeightSpec(self.names["router"], (p.n_experts, p.dim), ("normal", 0.3)),
+                WeightSpec(self.names["w1"], (p.n_experts, p.ffn_dim, p.dim), ("normal", 0.1)),
+                WeightSpec(self.names["w2"], (p.n_experts, p.dim, p.ffn_dim), ("normal", 0.1))]
+
+    def bind(self, tensors, ops):
+        self.router, self.w1, self.w2 = (tensors[k].float() for k in ("router", "w1", "w2"))
+
+    def forward(self, x, ctx):
+        xf = x.float()
+        gate = torch.softmax(xf @ self.router.T, -1)
+        y = torch.zeros_like(xf)
+        for e in range(self.params.n_experts):
+            y += gate[:, e:e + 1] * (torch.relu(xf @ self.w1[e].T) @ self.w2[e].T)
+        return y.to(x.dtype)
+
+
+@dataclass(frozen=True)
+class PartialRopeParams:
+    head_dim: int
+    theta: float
+    rotated_pairs: int  # the first pairs are rotated, the rest are left as they are
+
+
+class PartialRope(PositionEncoding):
+    def table(self, device):
+        p = self.params
+        j = torch.arange(p.head_dim // 2, dtype=torch.float32)
+        freqs = p.theta ** (-2.0 * j / (2 * p.rotated_pairs))
+        freqs[p.rotated_pairs:] = 0.0  # angle 0: not rotated
+        return freqs.to(device)
+
+
+class ToyLayerNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * w, float32 arithmetic."""
+
+    def weight_specs(self):
+        return [WeightSpec(self.names["weight"], (self.params.dim,), ("ones",))]
+
+    def bind(self, tensors, ops):
+        self.ops = ops
+        self.weight = tensors["weight"].float()
+
+    def forward(self, x, out_dtype=None, rows=None):
+        xf = x.float() if rows is None else x.float()[rows.long()]
+        y = (xf - xf.mean(-1, keepdim=True)) * torch.rsqrt(xf.var(-1, unbiased=False, keepdim=True) + self.params.eps)
+        return (y * self.weight).to(out_dtype or self.ops.act_dtype)
+
+
+class ParallelBlock(Block):
+    """h = h + mixer(norm(h)) + ffn(norm(h)): one norm, both parts read it."""
+
+    def forward(self, h, pending, ctx, memory):
+        if pending is not None:
+            h.add_(pending.float())
+        a = self.mixer_norm.forward(h)
+        return h, self.mixer.forward(a, ctx, memory).float() + self.ffn.forward(a, ctx).float()
+
+
+def _toy2_args(cfg):
+    d, v = cfg["hidden_size"], cfg["vocab_size"]
+
+    def attn(i, position):
+        return PartSpec("gqa_attention", AttentionParams(d, 3, 3, 16, position),
+                        {"wq": f"l{i}.q", "wk": f"l{i}.k", "wv": f"l{i}.v", "wo": f"l{i}.o"})
+
+    ln = lambda name: PartSpec("toy_layernorm", RMSNormParams(d, 1e-3), {"weight": name})
+    rms = lambda name: PartSpec("rmsnorm", RMSNormParams(d, 1e-5), {"weight": name})
+    routed = PartSpec("toy_routed", RoutedParams(d, 40, 3), {"router": "l0.r", "w1": "l0.e1", "w2": "l0.e2"})
+    swiglu = PartSpec("swiglu", SwiGLUParams(d, 72), {"w1": "l1.w1", "w3": "l1.w3", "w2": "l1.w2"})
+    layers = (
+        LayerSpec("toy_parallel", attn(0, PartSpec("toy_partial_rope", PartialRopeParams(16, 100.0, 5))), ln("l0.n"),
+                  routed, ln("l0.n")),
+        LayerSpec("prenorm", attn(1, PartSpec("none", NoPositionParams())), rms("l1.n1"), swiglu, rms("l1.n2")),
+    )
+    return ModelArgs("Toy2ForCausalLM", d, v, cfg["max_position_embeddings"], False, "emb", "out", layers,
+                     (ScheduleEntry(0), ScheduleEntry(1)), rms("final"))
+
+
+def _toy2_plain(w, tokens):
+    t = len(tokens)
+    pos = torch.arange(t)
+    h = w["emb"][torch.tensor(tokens)]
+    # layer 0: parallel block, layer norm, partial rotation, routed feed-forward
+    a = (h - h.mean(-1, keepdim=True)) * torch.rsqrt(h.var(-1, unbiased=False, keepdim=True) + 1e-3) * w["l0.n"]
+    j = torch.arange(8, dtype=torch.float64)
+    freqs = 100.0 ** (-2.0 * j / 10)
+    freqs[5:] = 0.0
+    q = pl.apply_rope((a @ pl.permute_qk_rows(w["l0.q"], 3).T).view(t, 3, 16), pos, freqs)
+    k = pl.apply_rope((a @ pl.permute_qk_rows(w["l0.k"], 3).T).view(t, 3, 16), pos, freqs)
+    v = (a @ w["l0.v"].T).view(t, 3, 16)
+    mix = pl.causal_attention(q, k, v, 0.25).reshape(t, 48) @ w["l0.o"].T
+    gate = torch.softmax(a @ w["l0.r"].T, -1)
+    ffn = sum(gate[:, e:e + 1] * (torch.relu(a @ w["l0.e1"][e].T) @ w["l0.e2"][e].T) for e in range(3))
+    h = h + mix + ffn
+    # layer 1: the usual block without a position encoding
+    a = pl.rmsnorm(h, w["l1.n1"], 1e-5)
+    q, k, v = ((a @ w[f"l1.{n}"].T).view(t, 3, 16) for n in "qkv")
+    h = h + pl.causal_attention(q, k, v, 0.25).reshape(t, 48) @ w["l1.o"].T
+    h = h + pl.swiglu(pl.rmsnorm(h, w["l1.n2"], 1e-5), w["l1.w1"], w["l1.w3"], w["l1.w2"])
+    return pl.rmsnorm(h, w["final"], 1e-5) @ w["out"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_architecture_with_routing_and_other_parts(tmp_path, dtype):
+    """A feed-forward with routing, a position encoding, a norm and a block arrangement that
+    the package does not have, registered here, built from a model folder and stepped in
+    mixed batches, against the same model written out plainly."""
+    from safetensors.torch import load_file
+    from fastgen_b200.weights import write_random_model
+
+    register_feed_forward("toy_routed", RoutedFeedForward)
+    register_position("toy_partial_rope", PartialRope)
+    register_norm("toy_layernorm", ToyLayerNorm)
+    register_block("toy_parallel", ParallelBlock)
+    register_architecture("Toy2ForCausalLM", _toy2_args)
+    cfg = dict(architectures=["Toy2ForCausalLM"], hidden_size=48, vocab_size=83, max_position_embeddings=128)
+    model_dir = write_random_model(tmp_path / "toy2", cfg, seed=5, norm_jitter=0.1, std=0.1)
+    w = {k: v.double() for k, v in load_file(str(model_dir / "model.safetensors")).items()}
+    reqs = {f"u{i}": H.random_tokens(83, n, 70 + i) for i, n in enumerate([5, 40, 17, 64, 9])}
+    steps = H.plan_mixed(reqs, seed=9, max_live=3)
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page_size=8,
+                                   max_tokens=H.max_live_tokens(steps, 8), max_requests=3)
+    got = H.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        ref = _toy2_plain(w, toks).numpy()
         for p, row in got[rid].items():
             err = np.abs(row - ref[p]).max()
             tol = 1e-4 if dtype == torch.float32 else 0.02 * max(1.0, np.abs(ref[p]).max())
