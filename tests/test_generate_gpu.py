@@ -137,6 +137,41 @@ def test_sync_freq_does_not_change_tokens(tmp_path):
             assert out[i] == want, f"sync_freq {freq}, request {i}"
 
 
+@pytest.mark.parametrize("sampling", [False, True])
+def test_many_requests_under_preemption_keep_their_tokens(tmp_path, sampling):
+    """Forty requests of random lengths through a cache that holds a few of them: requests are
+    preempted and recomputed again and again (decode runs of 10 steps included), and in
+    float32 every request still gets the tokens it gets with room for all."""
+    import random
+    from fastgen_b200.engine import Fastgen, GenArgs, HfLoader, Packet
+
+    model_dir = H.make_model_dir(tmp_path, "tiny_d")
+    rng = random.Random(5)
+    prompts = [H.random_tokens(300, rng.randint(1, 200), 100 + i) for i in range(40)]
+    gens = [rng.randint(1, 120) for _ in prompts]
+
+    def run(max_seq):
+        fg = Fastgen.build(HfLoader(model_dir), GenArgs(use_sampling=sampling, temperature=0.9, top_p=0.95,
+                                                        cache_block=64, max_seq=max_seq, max_batch=16, max_prefill=128,
+                                                        seed=3), device="cuda:0", dtype=torch.float32)
+        q = queue.Queue()
+        for i, (p, g) in enumerate(zip(prompts, gens)):
+            q.put(Packet(thread_id=i, tokens=p, max_gen=g))
+        q.put(None)
+        out = {p.thread_id: p.tokens for p in fg.generate(q)}
+        n = fg.scheduler.n_preemptions
+        fg.engine.cache.check()
+        assert fg.engine.cache.n_live == 0
+        fg.destroy()
+        return out, n
+
+    roomy, n_roomy = run(16 * 384)
+    tight, n_tight = run(6 * 64 + 320)
+    assert n_roomy == 0 and n_tight >= 5
+    assert all(len(roomy[i]) == gens[i] for i in roomy)
+    assert tight == roomy
+
+
 def test_stop_token_and_errors(tmp_path):
     model_dir = H.make_model_dir(tmp_path, "tiny_a")
     model = pl.read_model(model_dir)
