@@ -8,6 +8,14 @@
 // 128-byte swizzled, which ldmatrix then reads without bank conflicts.  The
 // pool is described by a 5-d tensor map [layer, page, kv head, slot, element].
 //
+// Two kernels for single tokens: attention_decode_tma_kernel, one block per (request,
+// kv head, split), for steps with few such items; and
+// attention_decode_persistent_kernel, whose blocks stay on their SM and walk the items
+// that exist (a producer warp streams keys and values through a ring of slots ahead of
+// four consumer warps), for steps with many.  Both leave partials per split in scratch
+// for attention_combine_kernel.  The file also holds the mma.sync prompt kernel on the
+// same TMA tiles (attention_prefill_tma_kernel), used where tcgen05 is not.
+//
 // Needs head sizes that are multiples of 64, pages of a power of two >= 8 slots
 // and groups of at most 16 query heads; other shapes use the cp.async kernel.
 #pragma once
