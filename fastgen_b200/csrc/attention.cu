@@ -69,9 +69,30 @@ extern "C" int fg_attention_prefill_rows() { return fg_mma::PREFILL_ROWS; }
 extern "C" int fg_attention_decode_split() { return fg_mma::DECODE_SPLIT; }
 
 // Floats of scratch that fg_attention_decode_bf16 needs.
-extern "C" long long fg_attention_decode_scratch_floats(int n_seqs, int max_splits, int n_heads) {
-  return (long long)n_seqs * max_splits * n_heads * fg_mma::part_stride<FG_HEAD_DIM>();
+// The scratch opens with FIRST_PAIR_INTS ints (for every request the number of (request,
+// split) pairs before it, written by the persistent kernel for the merge of the splits), then
+// the partials.  max_pairs bounds the pairs of a step (0: n_seqs * max_splits).
+constexpr int FIRST_PAIR_INTS = 1024;
+
+extern "C" long long fg_attention_decode_scratch_floats(int n_seqs, int max_splits, int n_heads, long long max_pairs) {
+  const long long all = (long long)n_seqs * max_splits;
+  if (max_pairs <= 0 || max_pairs > all) max_pairs = all;
+  return FIRST_PAIR_INTS + max_pairs * n_heads * fg_mma::part_stride<FG_HEAD_DIM>();
 }
+
+[[maybe_unused]] static int sm_count() {
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n_sms;
+}
+
+// Whether single tokens of these shapes go to the persistent kernel (whose launch does not
+// depend on the requests' lengths and whose partials are numbered by pairs).
+extern "C" int fg_attention_decode_is_persistent(int n_seqs, int n_heads, int n_kv_heads, int page_size);
 
 // Prompt portions.  Tiles hold max(1, 64 / hpb) consecutive tokens of one request,
 // hpb = min(group, 64); grid.z walks the group in slices of hpb heads.
@@ -125,9 +146,9 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                "fg_attention_decode_bf16: %d heads over %d kv heads, %d sequences", n_heads, n_kv_heads, n_seqs);
   FG_CHECK_ARG(max_splits > 0, "fg_attention_decode_bf16: max_splits must be positive");
   FG_CHECK_ARG(scratch != nullptr &&
-                   scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads),
+                   scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads, 0),
                "fg_attention_decode_bf16: scratch of %lld floats is too small (%lld needed)", scratch_floats,
-               fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads));
+               fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads, 0));
   FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
                "fg_attention_decode_bf16: queries must be 16-byte aligned with a row stride multiple of 8");
   const int group = n_heads / n_kv_heads;
@@ -140,6 +161,7 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
     attr_set = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
+  scratch += FIRST_PAIR_INTS;
   dim3 grid(max_splits, n_kv_heads, n_seqs);
   kern<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
                                         (const __nv_bfloat16*)v_pages, block_table, table_width, page_size,
@@ -148,7 +170,7 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
   FG_CHECK_LAUNCH("fg_attention_decode_bf16");
   dim3 cgrid(n_heads, n_seqs);
   attention_combine_kernel<FG_HEAD_DIM><<<cgrid, 128, 0, stream>>>(
-      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, status);
+      scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, nullptr, status);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
 }
@@ -169,8 +191,8 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
                                             int n_pages, const int* pos, const int* seq_req,
                                             const int* seq_tok, int n_seqs, int n_heads, int n_kv_heads,
                                             int head_dim, int window, float scale, float* scratch,
-                                            long long scratch_floats, int max_splits, int* status,
-                                            cudaStream_t stream) {
+                                            long long scratch_floats, int max_splits, long long max_pairs,
+                                            int* status, cudaStream_t stream) {
   using namespace fg_tma;
   if (n_seqs == 0) return 0;
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_decode_tma_bf16: library built for head size %d, got %d",
@@ -181,33 +203,23 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
   FG_CHECK_ARG(group <= DECODE_ROWS, "fg_attention_decode_tma_bf16: groups of %d heads are not supported", group);
   FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
                "fg_attention_decode_tma_bf16: pages of %d slots are not supported", page_size);
-  FG_CHECK_ARG(max_splits > 0 && scratch != nullptr &&
-                   scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads),
-               "fg_attention_decode_tma_bf16: scratch of %lld floats is too small", scratch_floats);
+  FG_CHECK_ARG(max_splits > 0 && scratch != nullptr, "fg_attention_decode_tma_bf16: no scratch");
   FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
                "fg_attention_decode_tma_bf16: queries must be 16-byte aligned with a row stride multiple of 8");
   CUtensorMap km, vm;
   memcpy(&km, k_map, sizeof(CUtensorMap));
   memcpy(&vm, v_map, sizeof(CUtensorMap));
-  constexpr size_t smem = decode_tma_smem_bytes<FG_HEAD_DIM>();
-  auto kern = attention_decode_tma_kernel<FG_HEAD_DIM>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
-  // several splits for every SM: the persistent kernel (one block an SM, a producer warp
-  // a stage ahead of the consumers); fewer: one block a split, three blocks an SM
-  const long long items = (long long)max_splits * n_kv_heads * n_seqs;
-  static int n_sms = 0;
-  if (n_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  const size_t psmem = decode_persistent_smem_bytes<FG_HEAD_DIM>(group);
-  if (items >= 4 * n_sms && group <= PS_MAX_GROUP && n_seqs <= PS_MAX_SEQS && psmem <= 227 * 1024 - 4352 - 256) {
+  int* first_pair = reinterpret_cast<int*>(scratch);
+  float* partials = scratch + FIRST_PAIR_INTS;
+  const int* combine_pairs = nullptr;
+  if (fg_attention_decode_is_persistent(n_seqs, n_heads, n_kv_heads, page_size)) {
+    // Blocks that stay on their SM (a producer warp ahead of four consumer warps) walk the
+    // (request, split, kv head) items that exist; the launch does not depend on the lengths.
+    const long long all = (long long)n_seqs * max_splits;
+    if (max_pairs <= 0 || max_pairs > all) max_pairs = all;
+    FG_CHECK_ARG(scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads, max_pairs),
+                 "fg_attention_decode_tma_bf16: scratch of %lld floats is too small", scratch_floats);
+    const size_t psmem = decode_persistent_smem_bytes<FG_HEAD_DIM>(group);
     auto pkern = attention_decode_persistent_kernel<FG_HEAD_DIM>;
     static size_t pattr_set = 0;
     if (pattr_set < psmem) {
@@ -215,22 +227,42 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
       FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
       pattr_set = psmem;
     }
-    fg_launch_pdl(pkern, dim3(ps_blocks_per_sm<FG_HEAD_DIM>() * n_sms), dim3(PS_THREADS), psmem, stream, km, vm, layer, (const __nv_bfloat16*)q,
-                  q_stride, block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_seqs, n_heads,
-                  n_kv_heads, group, window, scale * 1.4426950408889634f, scratch, max_splits, status);
+    fg_launch_pdl(pkern, dim3(ps_blocks_per_sm<FG_HEAD_DIM>() * sm_count()), dim3(PS_THREADS), psmem, stream, km, vm,
+                  layer, (const __nv_bfloat16*)q, q_stride, block_table, table_width, page_size, n_pages, pos,
+                  seq_req, seq_tok, n_seqs, n_heads, n_kv_heads, group, window, scale * 1.4426950408889634f,
+                  partials, first_pair, max_pairs, max_splits, status);
+    combine_pairs = first_pair;
   } else {
+    // one block per (request, kv head, split): larger groups of heads, very many requests
+    FG_CHECK_ARG(scratch_floats >= fg_attention_decode_scratch_floats(n_seqs, max_splits, n_heads, 0),
+                 "fg_attention_decode_tma_bf16: scratch of %lld floats is too small", scratch_floats);
+    constexpr size_t smem = decode_tma_smem_bytes<FG_HEAD_DIM>();
+    auto kern = attention_decode_tma_kernel<FG_HEAD_DIM>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      FG_CHECK_ARG(e == cudaSuccess, "fg_attention_decode_tma_bf16: shared memory: %s", cudaGetErrorString(e));
+      attr_set = true;
+    }
     dim3 grid(max_splits, n_kv_heads, n_seqs);
     fg_launch_pdl(kern, grid, dim3(THREADS), smem, stream, km, vm, layer, (const __nv_bfloat16*)q, q_stride,
                   block_table, table_width, page_size, n_pages, pos, seq_req, seq_tok, n_heads, group, window,
-                  scale * 1.4426950408889634f, scratch, max_splits, status);
+                  scale * 1.4426950408889634f, partials, max_splits, status);
   }
   FG_CHECK_LAUNCH("fg_attention_decode_tma_bf16");
   dim3 cgrid(n_heads, n_seqs);
   fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(128), 0, stream,
-                (const float*)scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
-                max_splits, status);
+                (const float*)partials, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
+                max_splits, combine_pairs, status);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
+}
+
+extern "C" int fg_attention_decode_is_persistent(int n_seqs, int n_heads, int n_kv_heads, int page_size) {
+  (void)page_size;
+  const int group = n_kv_heads > 0 ? n_heads / n_kv_heads : 0;
+  return group >= 1 && group <= fg_tma::PS_MAX_GROUP && n_seqs <= fg_tma::PS_MAX_SEQS &&
+         fg_tma::decode_persistent_smem_bytes<FG_HEAD_DIM>(group) <= 227 * 1024 - 4352 - 256;
 }
 
 extern "C" int fg_attention_prefill_tma_rows() { return fg_tma::PF_ROWS; }
@@ -326,4 +358,5 @@ extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
 #else
 extern "C" int fg_attention_decode_tma_supported() { return 0; }
 extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
+extern "C" int fg_attention_decode_is_persistent(int, int, int, int) { return 0; }
 #endif

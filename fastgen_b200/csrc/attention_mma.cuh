@@ -542,7 +542,10 @@ __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, int out_stride,
                          const int* __restrict__ pos, const int* __restrict__ seq_req,
                          const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
-                         int* status) {
+                         const int* first_pair, int* status) {
+  // first_pair (written by the kernel before, so no __restrict__): null, or for every
+  // request the number of (request, split) pairs before it; the partials are then
+  // numbered [pair][head] (only the splits that exist), else [request][head][split].
   constexpr int CHUNK = 128;  // splits whose weights are staged at a time
   __shared__ float w_s[CHUNK];
   __shared__ float red[4];
@@ -564,11 +567,15 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
     if (tid == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
     s_hi = max_splits - 1;
   }
-  const float* base = scratch + ((size_t)seq * n_heads + head) * max_splits * part_stride<HD>();
   constexpr int PS = part_stride<HD>();
+  // base[s * step]: the partial of split s
+  const size_t step = first_pair != nullptr ? (size_t)n_heads * PS : PS;
+  const float* base = first_pair != nullptr
+                          ? scratch + ((size_t)(first_pair[seq] - s_lo) * n_heads + head) * PS
+                          : scratch + ((size_t)seq * n_heads + head) * max_splits * PS;
   // the overall maximum
   float mm = -INFINITY;
-  for (int s = s_lo + tid; s <= s_hi; s += blockDim.x) mm = fmaxf(mm, base[(size_t)s * PS + HD]);
+  for (int s = s_lo + tid; s <= s_hi; s += blockDim.x) mm = fmaxf(mm, base[(size_t)s * step + HD]);
   mm = warp_max(mm);
   if (lane == 0) red[warp] = mm;
   __syncthreads();
@@ -581,19 +588,19 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
     const int n = min(CHUNK, s_hi - c0 + 1);
     __syncthreads();
     if (tid < n) {
-      const float ms = base[(size_t)(c0 + tid) * PS + HD];
+      const float ms = base[(size_t)(c0 + tid) * step + HD];
       w_s[tid] = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
     }
     __syncthreads();
     // every thread accumulates the sum in the same ascending order
-    for (int s = 0; s < n; ++s) ll += w_s[s] * base[(size_t)(c0 + s) * PS + HD + 1];
+    for (int s = 0; s < n; ++s) ll += w_s[s] * base[(size_t)(c0 + s) * step + HD + 1];
 #pragma unroll
     for (int i = 0; i < (HD + 127) / 128; ++i) {
       const int d = tid + i * 128;
       if (d < HD) {
         float a = acc[i];
 #pragma unroll 8
-        for (int s = 0; s < n; ++s) a += w_s[s] * base[(size_t)(c0 + s) * PS + d];
+        for (int s = 0; s < n; ++s) a += w_s[s] * base[(size_t)(c0 + s) * step + d];
         acc[i] = a;
       }
     }

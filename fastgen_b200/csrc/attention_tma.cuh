@@ -308,7 +308,8 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
                                    int n_pages, const int* __restrict__ pos, const int* __restrict__ seq_req,
                                    const int* __restrict__ seq_tok, int n_seqs, int n_heads, int n_kv_heads,
                                    int group, int window, float scale_log2, float* __restrict__ scratch,
-                                   int max_splits, int* status) {
+                                   int* __restrict__ first_pair_out, long long max_pairs, int max_splits,
+                                   int* status) {
   static_assert(HD % 64 == 0, "tiled loads take 64-element halves");
   constexpr int HALVES = HD / 64;
   constexpr int SLOT_BYTES = HALVES * HALF_BYTES;  // keys (or values) of one split
@@ -371,7 +372,17 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
 
   const int box_rows = min(page_size, SPLIT);
   const int n_boxes = SPLIT / box_rows;
-  const int total = s_cum[n_seqs] * n_kv_heads;
+  // the (request, split) pairs also number the partials, [pair][head]: what the merge of the
+  // splits needs to find them goes to global memory
+  if (blockIdx.x == 0)
+    for (int sq = tid; sq <= n_seqs; sq += PS_THREADS) first_pair_out[sq] = s_cum[sq];
+  int n_pairs = s_cum[n_seqs];
+  if (n_pairs > max_pairs) {
+    // the scratch was sized for fewer: report instead of writing past it
+    if (tid == 0 && blockIdx.x == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
+    n_pairs = (int)max_pairs;
+  }
+  const int total = n_pairs * n_kv_heads;
   // Both kinds of warps walk the same list.
   auto item_of = [&](int item, int& seq, int& g, int& split, int& p, int& k_begin) -> bool {
     g = item % n_kv_heads;
@@ -578,7 +589,7 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
           acc += f * wo[(w * group + r) * MLD + d];
           ll += f * wl[w * PS_MAX_GROUP + r];
         }
-        float* dst = scratch + (((size_t)seq * n_heads + g * group + r) * max_splits + split) * part_stride<HD>();
+        float* dst = scratch + ((size_t)(item / n_kv_heads) * n_heads + g * group + r) * part_stride<HD>();
         dst[d] = acc;
         if (d == 0) {
           dst[HD] = mm;

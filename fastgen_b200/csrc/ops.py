@@ -66,7 +66,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
-                                     _F, _P, ctypes.c_longlong, _I, _P, _P],
+                                     _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P],
+    "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
 }
 
 SKINNY_MAX_M = 8      # most tokens the weight-streaming product is used for (it takes up to 32)
@@ -124,7 +125,7 @@ def attn(head_dim: int):
     if lib is None:
         lib = build.attention_library(head_dim)
         _declare(lib, _ATTN_SIGNATURES)
-        lib.fg_attention_decode_scratch_floats.argtypes = [_I, _I, _I]
+        lib.fg_attention_decode_scratch_floats.argtypes = [_I, _I, _I, ctypes.c_longlong]
         lib.fg_attention_decode_scratch_floats.restype = ctypes.c_longlong
         assert lib.fg_attention_rows_per_block() == SIMT_ROWS
         assert lib.fg_attention_prefill_rows() == PREFILL_ROWS
@@ -452,19 +453,25 @@ class Ops:
         singles = ctx.single_tokens()
         if singles.n:
             max_splits = max(1, -(-singles.max_len // DECODE_SPLIT))
-            floats = lib.fg_attention_decode_scratch_floats(singles.n, max_splits, n_heads)
+            tma = use_tma and n_heads // n_kv_heads <= 16
+            # the persistent kernel numbers its partials by the (request, split) pairs that
+            # exist: the scratch follows the keys in the cache, not requests x longest request
+            pairs = 0
+            if tma and lib.fg_attention_decode_is_persistent(singles.n, n_heads, n_kv_heads, page_size):
+                pairs = min(singles.n * max_splits, singles.max_pairs or singles.n * max_splits)
+            floats = lib.fg_attention_decode_scratch_floats(singles.n, max_splits, n_heads, pairs)
             scratch = self._decode_scratch(floats)
-            tail = (_ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
-                    int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits,
-                    _ptr(self.status), _stream())
-            if use_tma and n_heads // n_kv_heads <= 16:
+            head = (_ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
+                    int(window or 0), float(scale), _ptr(scratch), scratch.numel(), max_splits)
+            if tma:
                 _check(lib, lib.fg_attention_decode_tma_bf16(
                     _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[0].ptr,
                     memory.tensor_maps[1].ptr, memory.layer_index, _ptr(block_table),
-                    block_table.shape[1], page_size, k_pages.shape[0], _ptr(ctx.pos), *tail))
+                    block_table.shape[1], page_size, k_pages.shape[0], _ptr(ctx.pos), *head, pairs,
+                    _ptr(self.status), _stream()))
             else:
                 _check(lib, lib.fg_attention_decode_bf16(
-                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *tail))
+                    _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common, *head, _ptr(self.status), _stream()))
             Ops.launches += 1  # the combine kernel
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,

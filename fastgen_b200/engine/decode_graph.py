@@ -35,9 +35,10 @@ _RING = 8
 
 
 class _Bucket:
-    def __init__(self, size: int, max_len: int, device) -> None:
+    def __init__(self, size: int, max_len: int, max_pairs: int, device) -> None:
         self.size = size
         self.max_len = max_len  # positions the captured launch grids cover
+        self.max_pairs = max_pairs  # (request, stretch of 128 positions) pairs the scratch holds
         # one packed buffer: tokens | pos | req | arange | ones
         # a ring of pinned staging buffers: a buffer is rewritten only after the
         # copy that last read it has run, so the host may run ahead of the device
@@ -63,7 +64,7 @@ class _Bucket:
         tiles = AttentionTiles(ctx.req, self.dev[3 * n : 4 * n], self.dev[4 * n :], n)
         none = AttentionTiles(None, None, None, 0)
         ctx.attention_tiles = lambda tokens_per_tile, min_tokens=1: tiles if min_tokens <= 1 else none
-        singles = SingleTokens(ctx.req, self.dev[3 * n : 4 * n], n, self.max_len)
+        singles = SingleTokens(ctx.req, self.dev[3 * n : 4 * n], n, self.max_len, self.max_pairs)
         ctx.single_tokens = lambda: singles
         return ctx
 
@@ -76,7 +77,13 @@ class DecodeGraphs:
         self.memories = engine.memories
         self.device = engine.device
         self.sizes = bucket_sizes(max_batch, num_graphs)
-        self.buckets: Dict[tuple, _Bucket] = {}
+        # A graph serves every context length: its launches cover the longest request the
+        # cache admits, and kernels whose work follows the lengths (the persistent
+        # single-token attention) read them from the positions.  The keys the cache can
+        # hold bound the partial results of a step.
+        self.max_len = engine.max_length
+        self.cache_tokens = max((g.pool.n_pages * g.page_size for g in engine.cache.groups), default=0)
+        self.buckets: Dict[int, _Bucket] = {}
         self.pool = None
         self.capture_stream = None
         self.warmed = set()  # batch sizes that ran once outside a capture
@@ -89,12 +96,10 @@ class DecodeGraphs:
         visit the host)."""
         n = len(positions)
         size = self.sizes[bisect.bisect_left(self.sizes, n)]
-        # launch grids cover a power-of-two number of key splits
-        splits = -(-(max(positions) + 1) // DECODE_SPLIT)
-        splits = 1 << (splits - 1).bit_length()
-        b = self.buckets.get((size, splits))
+        b = self.buckets.get(size)
         if b is None:
-            b = self.buckets[(size, splits)] = _Bucket(size, splits * DECODE_SPLIT, self.device)
+            pairs = min(size * -(-self.max_len // DECODE_SPLIT), self.cache_tokens // DECODE_SPLIT + size)
+            b = self.buckets[size] = _Bucket(size, self.max_len, pairs, self.device)
         slot = b.ring_next
         b.ring_next = (slot + 1) % _RING
         if b.ring_events[slot] is not None:

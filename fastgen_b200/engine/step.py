@@ -58,6 +58,10 @@ class SingleTokens:
     tok: Optional[torch.Tensor]
     n: int
     max_len: int
+    #: an upper bound on the (sequence, stretch of 128 cached positions) pairs of these
+    #: sequences together (0: unknown); kernels that keep partial results per pair size
+    #: their scratch by it
+    max_pairs: int = 0
 
 
 class StepContext:
@@ -112,19 +116,21 @@ class StepContext:
     def single_tokens(self) -> "SingleTokens":
         """The sequences that bring exactly one token (decoded tokens)."""
         if self._singles is None:
-            req, tok, max_len = [], [], 0
+            req, tok, max_len, pairs = [], [], 0, 0
             for b, slot in enumerate(self.host_seq_slot):
                 start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
                 if end - start == 1:
                     req.append(slot)
                     tok.append(start)
-                    max_len = max(max_len, self.host_seq_cached[b] + 1)
+                    length = self.host_seq_cached[b] + 1
+                    max_len = max(max_len, length)
+                    pairs += -(-length // 128)
             n = len(req)
             if n == 0:
                 self._singles = SingleTokens(None, None, 0, 0)
             else:
                 packed = torch.tensor(req + tok, dtype=torch.int32).to(self.device)
-                self._singles = SingleTokens(packed[:n], packed[n:], n, max_len)
+                self._singles = SingleTokens(packed[:n], packed[n:], n, max_len, pairs)
         return self._singles
 
 
