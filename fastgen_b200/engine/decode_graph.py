@@ -46,6 +46,7 @@ class _Bucket:
         self.ring_events = [None] * _RING
         self.ring_next = 0
         self.dev = torch.zeros(5 * size, dtype=torch.int32, device=device)
+        self.dev[2 * size : 3 * size] = -1  # until a step fills them, all lanes are padding
         self.dev[3 * size : 4 * size] = torch.arange(size, dtype=torch.int32, device=device)
         self.dev[4 * size :] = 1
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -96,10 +97,7 @@ class DecodeGraphs:
         visit the host)."""
         n = len(positions)
         size = self.sizes[bisect.bisect_left(self.sizes, n)]
-        b = self.buckets.get(size)
-        if b is None:
-            pairs = min(size * -(-self.max_len // DECODE_SPLIT), self.cache_tokens // DECODE_SPLIT + size)
-            b = self.buckets[size] = _Bucket(size, self.max_len, pairs, self.device)
+        b = self._bucket(size)
         slot = b.ring_next
         b.ring_next = (slot + 1) % _RING
         if b.ring_events[slot] is not None:
@@ -121,43 +119,61 @@ class DecodeGraphs:
         ev = torch.cuda.Event()
         ev.record()
         b.ring_events[slot] = ev
-        model, memories = self.model, self.memories
         if b.graph is None:
-            ctx = b.context(self.device)
-            if size not in self.warmed:
-                # once eagerly for a batch size (libraries load and choose their kernels,
-                # function attributes get set), then capture
-                model.forward(ctx, memories)
-                self.warmed.add(size)
-            graph = torch.cuda.CUDAGraph()
-            before = Ops.launches
-            # Captured by hand on a stream of its own: torch.cuda.graph() would also run the
-            # collector and empty the allocator's cache, tens of milliseconds a capture, and
-            # captures happen while requests are being served.  The collector stays off while
-            # capturing: destroying an old graph or freeing device memory in the middle of a
-            # capture would invalidate it.
-            if self.capture_stream is None:
-                self.capture_stream = torch.cuda.Stream(self.device)
-            gc_was_on = gc.isenabled()
-            gc.disable()
-            try:
-                self.capture_stream.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(self.capture_stream):
-                    kw = {} if self.pool is None else {"pool": self.pool}
-                    graph.capture_begin(**kw)
-                    try:
-                        b.logits = model.forward(ctx, memories)
-                    finally:
-                        graph.capture_end()
-                torch.cuda.current_stream().wait_stream(self.capture_stream)
-            finally:
-                if gc_was_on:
-                    gc.enable()
-            b.n_kernels = Ops.launches - before
-            if self.pool is None:
-                self.pool = graph.pool()
-            b.graph = graph
+            self._capture(b)
         b.graph.replay()
         Ops.launches += b.n_kernels
         self.replays += 1
         return b.logits[:n]
+
+    def _bucket(self, size: int) -> _Bucket:
+        b = self.buckets.get(size)
+        if b is None:
+            pairs = min(size * -(-self.max_len // DECODE_SPLIT), self.cache_tokens // DECODE_SPLIT + size)
+            b = self.buckets[size] = _Bucket(size, self.max_len, pairs, self.device)
+        return b
+
+    def capture_all(self) -> None:
+        """Capture the graph of every batch bucket now (the reference does so when it is
+        built, fastgen/generate.py:300-347), so that no step waits for a capture."""
+        for size in self.sizes:
+            b = self._bucket(size)
+            if b.graph is None:
+                self._capture(b)
+
+    def _capture(self, b: _Bucket) -> None:
+        model, memories, size = self.model, self.memories, b.size
+        ctx = b.context(self.device)
+        if size not in self.warmed:
+            # once eagerly for a batch size (libraries load and choose their kernels,
+            # function attributes get set), then capture
+            model.forward(ctx, memories)
+            self.warmed.add(size)
+        graph = torch.cuda.CUDAGraph()
+        before = Ops.launches
+        # Captured by hand on a stream of its own: torch.cuda.graph() would also run the
+        # collector and empty the allocator's cache, tens of milliseconds a capture, and
+        # captures happen while requests are being served.  The collector stays off while
+        # capturing: destroying an old graph or freeing device memory in the middle of a
+        # capture would invalidate it.
+        if self.capture_stream is None:
+            self.capture_stream = torch.cuda.Stream(self.device)
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            self.capture_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.capture_stream):
+                kw = {} if self.pool is None else {"pool": self.pool}
+                graph.capture_begin(**kw)
+                try:
+                    b.logits = model.forward(ctx, memories)
+                finally:
+                    graph.capture_end()
+            torch.cuda.current_stream().wait_stream(self.capture_stream)
+        finally:
+            if gc_was_on:
+                gc.enable()
+        b.n_kernels = Ops.launches - before
+        if self.pool is None:
+            self.pool = graph.pool()
+        b.graph = graph

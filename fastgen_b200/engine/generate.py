@@ -152,6 +152,9 @@ class Fastgen:
         )
         self.steps = 0
         self.step_log: List[dict] = []  # per step: times, token counts, bytes copied
+        if self.engine.graphs is not None:
+            # as the reference does when it is built (generate.py:300-347): no step waits for a capture
+            self.engine.graphs.capture_all()
 
     def destroy(self) -> None:
         """Free what the generator holds on the device."""
