@@ -51,6 +51,8 @@ class GenArgs:
     num_cuda_graphs: int = 16
 
     max_prefill: int = 8192  # tokens per step, prompt portions and decoded tokens together
+    min_prefill: int = 2048  # newly admitted prompts with fewer tokens than this together ...
+    min_prefill_batch: int = 1  # ... and fewer requests than this wait while others decode
     prefill_gb: float = 0.5  # used by the memory budget
     gpu_gb: float = 20  # ditto
 
@@ -148,7 +150,8 @@ class Fastgen:
             top_p=args.top_p, seed=args.seed, logprobs=args.logprobs,
         )
         self.scheduler = Scheduler(
-            self.engine.cache, self.max_batch, self.max_prefill, self.stop_tokens, args.max_gen
+            self.engine.cache, self.max_batch, self.max_prefill, self.stop_tokens, args.max_gen,
+            min_prefill=args.min_prefill, min_prefill_batch=args.min_prefill_batch,
         )
         self.steps = 0
         self.step_log: List[dict] = []  # per step: times, token counts, bytes copied
@@ -181,6 +184,7 @@ class Fastgen:
             except queue.Empty:
                 break
             if pkt is None:
+                self.scheduler.input_ended = True
                 return True
             # generate.py:790: a per-request temperature of 0 falls back to the default
             temp = pkt.temperature or self.gen_args.temperature

@@ -76,6 +76,8 @@ class Scheduler:
         token_budget: int,
         stop_tokens: Sequence[int] = (),
         max_gen: Optional[int] = None,
+        min_prefill: int = 0,
+        min_prefill_batch: int = 1,
     ) -> None:
         if token_budget < 1:
             raise ValueError("the token budget of a step must be at least 1")
@@ -87,6 +89,12 @@ class Scheduler:
         self.capacity = min(
             [cache.max_length] + [g.pool.n_pages * g.page_size for g in cache.groups]
         )
+        # the reference's rule for batching prompts (generate.py:600-608): while requests are
+        # decoding and more input may come, fewer than ``min_prefill_batch`` newly admitted
+        # requests with fewer than ``min_prefill`` tokens together wait for company
+        self.min_prefill = min_prefill
+        self.min_prefill_batch = min_prefill_batch
+        self.input_ended = False  # set by the caller once no more requests will be added
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []  # in admission order
         self.finished: List[Request] = []
@@ -121,6 +129,18 @@ class Scheduler:
 
     # -- decisions ---------------------------------------------------------------
     def _admit(self) -> None:
+        n_before = len(self.running)
+        self._admit_all()
+        new = self.running[n_before:]
+        if (new and n_before > 0 and not self.input_ended and len(new) < self.min_prefill_batch
+                and sum(len(r) for r in new) < self.min_prefill):
+            # wait some more before prefilling: give slots and pages back, keep the order
+            for req in reversed(new):
+                self.cache.release(id(req))
+                self.waiting.appendleft(req)
+            del self.running[n_before:]
+
+    def _admit_all(self) -> None:
         while self.waiting and len(self.running) < self.max_batch:
             req = self.waiting[0]
             if self.cache.free_slots() == 0:

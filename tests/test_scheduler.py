@@ -174,3 +174,45 @@ def test_decode_runs_of_several_steps():
     assert sched.plan_decode_run(10) == 1 or cache.free_pages() == [0]
     c = sched.add("c", [1, 2, 3], max_gen=3)
     assert sched.plan_decode_run(10) == 1
+
+
+def test_min_prefill_batch_makes_short_prompts_wait_for_company():
+    """The reference's rule (generate.py:600-608): while requests decode and more input may
+    come, a lone newly admitted short prompt waits; it goes in with a second one, when the
+    input has ended, or when nothing is decoding."""
+    from fastgen_b200.cache import CacheManager
+    from fastgen_b200.parts import CacheSpec
+
+    def make():
+        cache = CacheManager([CacheSpec(1, 16)], [None], [None], page_size=8, n_pages=64, max_requests=8,
+                             max_length=256, dtype=None, device=None)
+        return Scheduler(cache, 8, 64, (), 4, min_prefill=32, min_prefill_batch=2), cache
+
+    def step(sched):
+        plan = sched.plan()
+        sched.commit(plan, [1] * sum(e.samples for e in plan))
+        return plan
+
+    sched, cache = make()
+    sched.add("first", [1] * 5)           # nothing is decoding: admitted alone
+    assert [e.request.thread_id for e in step(sched)] == ["first"]
+    sched.add("lone", [2] * 5)            # short, alone, others decode, input open: waits
+    assert [e.request.thread_id for e in step(sched)] == ["first"]
+    assert len(sched.waiting) == 1 and cache.n_live == 1
+    sched.add("second", [3] * 5)          # now two: both go in
+    assert sorted(e.request.thread_id for e in step(sched)) == ["first", "lone", "second"]
+    cache.check()
+
+    sched, cache = make()
+    sched.add("first", [1] * 5)
+    step(sched)
+    sched.add("long", [2] * 40)           # enough tokens by itself
+    assert sorted(e.request.thread_id for e in step(sched)) == ["first", "long"]
+
+    sched, cache = make()
+    sched.add("first", [1] * 5)
+    step(sched)
+    sched.add("lone", [2] * 5)
+    sched.input_ended = True              # no company will come
+    assert sorted(e.request.thread_id for e in step(sched)) == ["first", "lone"]
+    cache.check()
