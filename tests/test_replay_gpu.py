@@ -73,3 +73,41 @@ def test_trace_run_program(tmp_path, dtype):
     outputs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
     got = H.collect(steps, outputs)
     H.compare(model_dir, reqs, got, torch.float32 if dtype == "float32" else torch.bfloat16)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+def test_nothing_is_written_outside_the_fed_positions(tmp_path, name, dtype):
+    """Every slot of every page starts as a sentinel; after a prompt in portions and some
+    single tokens (captured graphs with padding lanes included), only the slots of the
+    request's own positions have changed, in its own pages."""
+    from fastgen_b200.engine import Engine, Model, StepEntry
+
+    model = Model.load(H.make_model_dir(tmp_path, name), dtype, "cuda:0")
+    page = PAGES[name]
+    engine = Engine(model, page_size=page, n_pages=12, max_requests=3, max_length=12 * page)
+    sentinel = 12345.0
+    for grp in engine.cache.groups:
+        grp.k_pages.fill_(sentinel)
+        grp.v_pages.fill_(sentinel)
+    vocab = H.CONFIGS[name][0]["vocab_size"]
+    toks = H.random_tokens(vocab, 2 * page + 5, 8)
+    engine.admit("a")
+    engine.admit("idle")  # a live request that brings nothing: its slot has no pages
+    cut = page + 3
+    engine.step([StepEntry("a", toks[:cut], [])])
+    engine.step([StepEntry("a", toks[cut:-4], [len(toks) - 4 - cut - 1])])
+    for t in toks[-4:]:
+        engine.step([StepEntry("a", [t], [0])])
+    engine.ops.check_status()
+    req = engine.cache.get("a")
+    assert req.length == len(toks)
+    for gi, grp in enumerate(engine.cache.groups):
+        own = req.pages[gi]
+        for pool in (grp.k_pages, grp.v_pages):  # [runs, pages, kv heads, page, head_dim]
+            touched = (pool != sentinel).any(-1).any(2).any(0).cpu()  # [pages, page]
+            for pg in range(pool.shape[1]):
+                logical = [lp for lp, p in own.items() if p == pg]
+                for slot in range(page):
+                    expect = bool(logical) and logical[0] * page + slot < len(toks)
+                    assert bool(touched[pg, slot]) == expect, (gi, pg, slot)
