@@ -18,7 +18,9 @@ parallelism) are not present; ``tp_mesh`` must be ``None``.
 from __future__ import annotations
 
 import logging
+import os
 import queue
+import tempfile
 import time
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -102,7 +104,10 @@ class Fastgen:
     @staticmethod
     def build(loader: HfLoader, gen_args: GenArgs, tp_mesh=None,
               device: Union[str, torch.device] = "cuda:0",
-              dtype: torch.dtype = torch.bfloat16) -> "Fastgen":
+              dtype: torch.dtype = torch.bfloat16, profile_sig: Optional[int] = None) -> "Fastgen":
+        """``profile_sig``: a signal number (the reference's default is SIGUSR2,
+        generate.py:145,166-172) on which a trace of the next scheduler iterations is
+        written, see ``request_profile``; ``None`` installs no handler."""
         if tp_mesh is not None:
             raise ValueError("this engine runs on one GPU; tp_mesh must be None")
         device = torch.device(device)
@@ -112,7 +117,13 @@ class Fastgen:
         stop_tokens = list(model.args.stop_tokens)
         if loader.has_tokenizer():
             stop_tokens = loader.load_tokenizer().stop_tokens or stop_tokens
-        return Fastgen(gen_args, model, stop_tokens)
+        fg = Fastgen(gen_args, model, stop_tokens)
+        if profile_sig is not None:
+            import signal
+
+            if signal.getsignal(profile_sig) is signal.SIG_DFL:  # never replace somebody's handler
+                signal.signal(profile_sig, lambda _signum, _frame: fg.request_profile())
+        return fg
 
     def __init__(self, args: GenArgs, model: Model, stop_tokens) -> None:
         self.gen_args = args
@@ -155,12 +166,57 @@ class Fastgen:
         )
         self.steps = 0
         self.step_log: List[dict] = []  # per step: times, token counts, bytes copied
+        # a trace on request (generate.py:187-196, 364-403): FG_PROFILE_ITERS scheduler iterations
+        # after ``request_profile()``, written as a chrome trace into FG_PROFILE_DIR
+        self.profile_iters = int(os.environ.get("FG_PROFILE_ITERS", "8"))
+        self.profile_dir = os.environ.get("FG_PROFILE_DIR", tempfile.gettempdir())
+        self.profile_state = "inactive"  # -> "requested" -> "active" -> "inactive"
+        self.profile_left = 0
+        self.profiler = None
+        self.last_profile: Optional[str] = None  # path of the trace written last
         if self.engine.graphs is not None:
             # as the reference does when it is built (generate.py:300-347): no step waits for a capture
             self.engine.graphs.capture_all()
 
+    def request_profile(self) -> None:
+        """Ask for a trace (CPU and CUDA activity) of the next ``FG_PROFILE_ITERS`` iterations
+        of the scheduler loop; it is written to ``FG_PROFILE_DIR`` when they are over."""
+        if self.profile_state == "inactive":
+            logger.info("Requesting profiling trace...")
+            self.profile_state = "requested"
+
+    def _profile_tick(self) -> None:
+        """Once per iteration of the scheduler loop."""
+        if self.profile_state == "requested":
+            from torch.profiler import ProfilerActivity, profile
+
+            self.profiler = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], with_stack=True)
+            self.profiler.__enter__()
+            self.profile_left = self.profile_iters
+            self.profile_state = "active"
+        elif self.profile_state == "active":
+            self.profile_left -= 1
+            if self.profile_left <= 0:
+                self._profile_stop()
+
+    def _profile_stop(self) -> None:
+        if self.profile_state != "active":
+            return
+        self.profile_state = "inactive"
+        prof, self.profiler = self.profiler, None
+        try:
+            prof.__exit__(None, None, None)
+            stamp = time.strftime("%H%M%S") + f".{int(time.time() * 1e6) % 1_000_000:06d}"
+            path = os.path.join(self.profile_dir, f"fastgen_b200_{os.getpid()}_{stamp}.json.gz")
+            prof.export_chrome_trace(path)
+            self.last_profile = path
+            logger.info("Profile chrome trace exported to %s", path)
+        except Exception as e:  # noqa: BLE001 - a failed trace must not end generation
+            logger.warning("Error while exporting profile trace: %r", e)
+
     def destroy(self) -> None:
         """Free what the generator holds on the device."""
+        self._profile_stop()
         self.engine = None
         self.scheduler = None
         self.sampler = None
@@ -244,6 +300,8 @@ class Fastgen:
         sched = self.scheduler
         eoq = False
         while not eoq or sched.has_work() or sched.finished:
+            if self.profile_state != "inactive":
+                self._profile_tick()
             eoq = self._pull(q, eoq)
             for req in sched.take_finished():
                 yield self._packet(req)

@@ -172,6 +172,29 @@ def test_many_requests_under_preemption_keep_their_tokens(tmp_path, sampling):
     assert tight == roomy
 
 
+def test_profile_trace_on_request(tmp_path, monkeypatch):
+    """request_profile() traces the next FG_PROFILE_ITERS iterations into FG_PROFILE_DIR."""
+    import gzip
+    from fastgen_b200.engine import Fastgen, GenArgs, HfLoader, Packet
+
+    monkeypatch.setenv("FG_PROFILE_ITERS", "3")
+    monkeypatch.setenv("FG_PROFILE_DIR", str(tmp_path))
+    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    fg = Fastgen.build(HfLoader(model_dir), GenArgs(use_sampling=False, max_gen=12, cache_block=8, max_seq=128,
+                                                    max_batch=2, sync_freq=1), device="cuda:0", dtype=torch.float32)
+    fg.request_profile()
+    q = queue.Queue()
+    q.put(Packet(thread_id=0, tokens=H.random_tokens(256, 9, 1)))
+    q.put(None)
+    out = list(fg.generate(q))
+    assert len(out) == 1 and len(out[0].tokens) == 12
+    assert fg.profile_state == "inactive" and fg.last_profile is not None
+    with gzip.open(fg.last_profile, "rt") as f:
+        head = f.read(4096)
+    assert "traceEvents" in head
+    fg.destroy()
+
+
 def test_stop_token_and_errors(tmp_path):
     model_dir = H.make_model_dir(tmp_path, "tiny_a")
     model = pl.read_model(model_dir)
