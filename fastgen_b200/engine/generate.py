@@ -134,6 +134,9 @@ class Fastgen:
         self.generating = False
         block = args.cache_block
         act_bytes = 4 if model.ops.act_dtype == torch.float32 else 2
+        self._last_used_gb: Optional[float] = None
+        logger.info("Initializing generator")
+        self._log_cuda_mem()
 
         # pages: from max_seq, or from the memory budget (generate.py:206-236)
         per_token = model.cache_bytes_per_token(act_bytes)
@@ -150,12 +153,19 @@ class Fastgen:
             raise RuntimeError("Not enough memory available for the generation caches")
         self.max_seq = max_seq
         self.max_prefill = args.max_prefill if args.max_prefill > 0 else mp.prefill_tokens
+        if args.max_prefill <= 0:
+            logger.info("Setting max prefill length to %d", self.max_prefill)
         self.max_batch = min(args.max_batch, max_seq // block)
+        if self.max_batch < args.max_batch:
+            logger.info("Adjusting max batch to %d", self.max_batch)
 
         self.engine = Engine(
             model, page_size=block, n_pages=max_seq // block, max_requests=self.max_batch,
             max_length=min(model.args.max_positions, max_seq),
         )
+        logger.info("Cache bytes per token: %d", per_token)
+        logger.info("Allocated kv cache: %d pages of %d tokens", max_seq // block, block)
+        self._log_cuda_mem()
         self.sampler = Sampler(
             self.ops, model.args.vocab_size, self.max_batch, use_sampling=args.use_sampling,
             top_p=args.top_p, seed=args.seed, logprobs=args.logprobs,
@@ -177,6 +187,17 @@ class Fastgen:
         if self.engine.graphs is not None:
             # as the reference does when it is built (generate.py:300-347): no step waits for a capture
             self.engine.graphs.capture_all()
+            logger.info("Created %d decoding graphs", len(self.engine.graphs.buckets))
+            self._log_cuda_mem()
+        logger.info("Done initializing")
+
+    def _log_cuda_mem(self) -> None:
+        used_gb = torch.cuda.memory_allocated(self.device) / 1e9
+        if self._last_used_gb is None:
+            logger.info("GPU memory: %.3fGB", used_gb)
+        else:
+            logger.info("GPU memory: %.3fGB (%+.3fGB)", used_gb, used_gb - self._last_used_gb)
+        self._last_used_gb = used_gb
 
     def request_profile(self) -> None:
         """Ask for a trace (CPU and CUDA activity) of the next ``FG_PROFILE_ITERS`` iterations
@@ -313,6 +334,11 @@ class Fastgen:
                 yield from self._decode_run(n_run)
                 continue
             plan = sched.plan()
+            if logger.isEnabledFor(logging.INFO):
+                logger.info("%d active requests", len(sched.running))
+                n_prompt = sum(len(e.tokens) for e in plan if not (len(e.tokens) == 1 and e.request.generated))
+                if n_prompt:
+                    logger.info("Prefilling %d tokens", n_prompt)
             if not plan:
                 if sched.has_work():
                     raise RuntimeError("the scheduler made no progress")  # cannot happen: see Scheduler.add
