@@ -377,6 +377,10 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, int by
 }
 // Bounded wait: gives up after ~2^22 polls, records it and lets the block finish
 // (its copies have either landed or the data is reported as unusable).
+//
+// A parity wait can only tell "this phase is over" from "not yet" while the waiter is less
+// than two completions behind the barrier: a barrier must not complete a second time before
+// a waiter of the first completion has looked (give every stage a barrier of its own).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, int* status) {
   for (int it = 0; it < (1 << 22); ++it) {
     uint32_t done;

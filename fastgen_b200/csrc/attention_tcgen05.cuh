@@ -73,7 +73,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   unsigned char* Vs = Ks + 2 * STAGE_BYTES;
   // full_k/full_v: a tile's keys/values have landed; s_done: its scores are in TMEM;
   // p_ready: all 128 softmax threads stored its probabilities; o_done: its P V is done
-  __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done;
+  __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int first_pos_s;
   constexpr int PAGE_STAGE = 256;
@@ -117,7 +117,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     // two of them: a softmax warp may be one tile ahead of another
     mbar_init(&p_ready[0], SOFTMAX_THREADS);
     mbar_init(&p_ready[1], SOFTMAX_THREADS);
-    mbar_init(&o_done, 1);
+    // one for the tiles of each parity: a waiter of O_t's completion can then never be two
+    // completions behind (the next one, O_{t+2}'s, needs that waiter's own work)
+    mbar_init(&o_done[0], 1);
+    mbar_init(&o_done[1], 1);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -215,7 +218,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
               tma_load_5d(kb + h * KV_HALF, &k_map, h * 64, slot, g, page, layer, &full_k[stage]);
-            if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+            if (t >= 2) mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1, status);
             mbar_arrive_expect(&full_v[stage], k_bytes);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
@@ -224,7 +227,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         } else {
           if (t >= 2) mbar_wait(&s_done[stage], ((t - 2) >> 1) & 1, status);
           load_tile(t, box_pages + staged, false);
-          if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+          if (t >= 2) mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1, status);
           load_tile(t, box_pages + staged, true);
         }
         if (++staged == tiles_per_fill) staged = 0;
@@ -236,7 +239,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const int* pages = box_pages + staged * n_boxes;
         if (t >= 2) mbar_wait(&s_done[t & 1], ((t - 2) >> 1) & 1, status);
         load_tile(t, pages, false);
-        if (t >= 2) mbar_wait(&o_done, (t - 2) & 1, status);
+        if (t >= 2) mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1, status);
         load_tile(t, pages, true);
         if (++staged == tiles_per_fill) staged = 0;
       }
@@ -271,7 +274,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         for (int j = 0; j < KEYS / 16; ++j)
           umma_f16_ts(tmem + COL_O, tmem + COL_S0 + stage * KEYS + j * 8, vd + (uint64_t)((j * 16 * 128) >> 4),
                       IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
-        umma_commit(&o_done);
+        umma_commit(&o_done[stage]);
       }
     }
     __syncwarp();
@@ -347,11 +350,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       l_run = l_run * alpha + sum;
       // P_t over the first 32 columns of S_t (this thread has read all of its row)
       tmem_st32_raw(s_addr, packed);
-      // Every completion of o_done is awaited in turn, needed or not: a parity wait can
-      // only tell "this phase is over" from "not yet" if the waiter never falls two
-      // phases behind.  O_{t-1} is complete after it; O is then rescaled where a row's
-      // reference maximum was raised (warp-uniform decision).
-      if (t > 0) mbar_wait(&o_done, (t - 1) & 1, status);
+      // O_{t-1} is complete after this wait; O is then rescaled where a row's reference
+      // maximum was raised (warp-uniform decision).  (The barrier of this parity completes
+      // next for O_{t+1}, which needs this thread's P_{t+1}: the wait cannot fall behind.)
+      if (t > 0) mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1, status);
       if (t > 0 && __any_sync(0xffffffffu, raise)) {
         tc_fence_after();
 #pragma unroll
@@ -367,7 +369,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       mbar_arrive(&p_ready[stage]);
     }
     // ---- O / l -> out ----
-    mbar_wait(&o_done, (n_tiles - 1) & 1, status);
+    mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, status);
     tc_fence_after();
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     __nv_bfloat16* dst = out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;

@@ -186,9 +186,9 @@ class Ops:
         self._stream_scratch = None
         self._stream_counters = None
         self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
-        # FG_STREAM_GEMM: "off" never uses the tcgen05 weight-streaming product, "all" uses it
-        # for every product of 9..256 tokens, default: where it measured faster than the library
-        self.stream_gemm = os.environ.get("FG_STREAM_GEMM", "auto")
+        # FG_STREAM_GEMM: "all" uses the tcgen05 weight-streaming product for every product of
+        # 9..256 tokens, "auto" where it measured faster than the library, default: never
+        self.stream_gemm = os.environ.get("FG_STREAM_GEMM", "off")
         # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -286,7 +286,10 @@ class Ops:
                 and w.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
         if self.stream_gemm == "all":
             return fits and SKINNY_MAX_M < m <= 256
-        return fits and 48 <= m <= 96 and n * k >= (1 << 28)
+        if self.stream_gemm == "auto":
+            # where it measured faster than the library: the vocabulary projection of 48..96 tokens
+            return fits and 48 <= m <= 96 and n * k >= (1 << 28)
+        return False
 
     def linear_stream(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
