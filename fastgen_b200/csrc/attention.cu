@@ -282,6 +282,7 @@ extern "C" int fg_attention_prefill_tma_bf16(const void* q, int q_stride, void* 
                FG_HEAD_DIM, head_dim);
   FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
                "fg_attention_prefill_tma_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG(n_tiles <= 65535, "fg_attention_prefill_tma_bf16: %d tiles in one call (at most 65535)", n_tiles);
   FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
                "fg_attention_prefill_tma_bf16: pages of %d slots are not supported", page_size);
   FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0,
@@ -299,7 +300,7 @@ extern "C" int fg_attention_prefill_tma_bf16(const void* q, int q_stride, void* 
     FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_tma_bf16: shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
+  dim3 grid(n_kv_heads, n_tiles, (group + hpb - 1) / hpb);
   kern<<<grid, PF_THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                            out_stride, block_table, table_width, page_size, n_pages, pos,
                                            tile_req, tile_tok0, tile_ntok, n_tiles, group, hpb, window,
@@ -327,6 +328,7 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
                FG_HEAD_DIM, head_dim);
   FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
                "fg_attention_prefill_tc5_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
+  FG_CHECK_ARG(n_tiles <= 65535, "fg_attention_prefill_tc5_bf16: %d tiles in one call (at most 65535)", n_tiles);
   FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
                "fg_attention_prefill_tc5_bf16: pages of %d slots are not supported", page_size);
   FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0,
@@ -344,7 +346,7 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
     FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_tc5_bf16: shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  dim3 grid(n_tiles, n_kv_heads, (group + hpb - 1) / hpb);
+  dim3 grid(n_kv_heads, n_tiles, (group + hpb - 1) / hpb);
   kern<<<grid, fg_tc5::THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                         out_stride, block_table, table_width, page_size, n_pages, pos, tile_req,
                                         tile_tok0, tile_ntok, n_tiles, group, hpb, window,

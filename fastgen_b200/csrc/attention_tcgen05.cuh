@@ -79,8 +79,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   constexpr int PAGE_STAGE = 256;
   __shared__ int box_pages[PAGE_STAGE];
 
-  const int tile = n_tiles_total - 1 - blockIdx.x;  // heavy tiles first
-  const int g = blockIdx.y, sub = blockIdx.z;
+  // The tile list is in ascending order of work and blockIdx.x runs fastest: all key/value
+  // heads of the heaviest tile start first, the lightest tiles fill the tail of the launch.
+  const int tile = n_tiles_total - 1 - blockIdx.y;
+  const int g = blockIdx.x, sub = blockIdx.z;
   const int b = tile_req[tile];
   const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

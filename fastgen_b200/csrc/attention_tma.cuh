@@ -681,9 +681,10 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   constexpr int PAGE_STAGE = 512;             // box page ids kept in shared memory at a time
   __shared__ int box_pages[PAGE_STAGE];
 
-  // the heaviest tiles (the latest tokens of long portions come last in the list) start first
-  const int tile = n_tiles_total - 1 - blockIdx.x;
-  const int g = blockIdx.y, sub = blockIdx.z;
+  // the tile list is in ascending order of work and blockIdx.x runs fastest: all key/value
+  // heads of the heaviest tile start first
+  const int tile = n_tiles_total - 1 - blockIdx.y;
+  const int g = blockIdx.x, sub = blockIdx.z;
   const int b = tile_req[tile];
   const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -90,7 +90,8 @@ class StepContext:
 
     def attention_tiles(self, tokens_per_tile: int, min_tokens: int = 1) -> AttentionTiles:
         """Tiles of at most ``tokens_per_tile`` consecutive tokens over the
-        sequences that bring at least ``min_tokens`` tokens."""
+        sequences that bring at least ``min_tokens`` tokens, in ascending order of
+        the number of keys a tile reads."""
         key = (tokens_per_tile, min_tokens)
         tiles = self._tiles.get(key)
         if tiles is None:
@@ -98,15 +99,21 @@ class StepContext:
         return tiles
 
     def _build_tiles(self, tpt: int, min_tokens: int) -> AttentionTiles:
-        req, tok0, ntok = [], [], []
+        tiles = []  # (keys the tile reads, slot, first token, tokens)
         for b, slot in enumerate(self.host_seq_slot):
             start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
             if end - start < min_tokens:
                 continue
+            cached = self.host_seq_cached[b]
             for t in range(start, end, tpt):
-                req.append(slot)
-                tok0.append(t)
-                ntok.append(min(tpt, end - t))
+                n_tok = min(tpt, end - t)
+                tiles.append((cached + t - start + n_tok, slot, t, n_tok))
+        # ascending by work: the kernels hand out the list from its end, so the tiles with
+        # the most keys start first and the short ones fill the tail of the launch
+        tiles.sort(key=lambda tile: tile[0])
+        req = [tile[1] for tile in tiles]
+        tok0 = [tile[2] for tile in tiles]
+        ntok = [tile[3] for tile in tiles]
         n = len(req)
         if n == 0:
             return AttentionTiles(None, None, None, 0)
