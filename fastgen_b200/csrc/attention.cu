@@ -314,21 +314,23 @@ extern "C" int fg_attention_prefill_tma_bf16(const void* q, int q_stride, void* 
 
 extern "C" int fg_attention_prefill_tc5_supported() { return 1; }
 
-// Prompt portions on tcgen05 / TMEM.  Same arguments and tiling (128 rows a block) as
-// fg_attention_prefill_tma_bf16; the tensor maps must have boxes of min(page, 64) rows.
+// Prompt portions on tcgen05 / TMEM.  Arguments and tiling (128 rows an item) as for
+// fg_attention_prefill_tma_bf16, plus `work_counter`: one unsigned int on the device that is
+// zero between launches (the kernel leaves it so) and is not shared by launches that can
+// run at the same time; the tensor maps must have boxes of min(page, 64) rows.
 extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* out, int out_stride,
                                              const void* k_map, const void* v_map, int layer,
                                              const int* block_table, int table_width, int page_size,
                                              int n_pages, const int* pos, const int* tile_req,
                                              const int* tile_tok0, const int* tile_ntok, int n_tiles,
                                              int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                             int* status, cudaStream_t stream) {
+                                             unsigned int* work_counter, int* status, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  FG_CHECK_ARG(work_counter != nullptr, "fg_attention_prefill_tc5_bf16: no work counter");
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tc5_bf16: library built for head size %d, got %d",
                FG_HEAD_DIM, head_dim);
   FG_CHECK_ARG(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_kv_heads <= 65535,
                "fg_attention_prefill_tc5_bf16: %d heads over %d kv heads", n_heads, n_kv_heads);
-  FG_CHECK_ARG(n_tiles <= 65535, "fg_attention_prefill_tc5_bf16: %d tiles in one call (at most 65535)", n_tiles);
   FG_CHECK_ARG(page_size >= 8 && (page_size & (page_size - 1)) == 0,
                "fg_attention_prefill_tc5_bf16: pages of %d slots are not supported", page_size);
   FG_CHECK_ARG(q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 && out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0,
@@ -346,11 +348,15 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
     FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_tc5_bf16: shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  dim3 grid(n_kv_heads, n_tiles, (group + hpb - 1) / hpb);
+  // two blocks an SM take the (tile, kv head, slice of the group) items from a counter
+  const long long total = (long long)n_tiles * n_kv_heads * ((group + hpb - 1) / hpb);
+  FG_CHECK_ARG(total < (1ll << 31), "fg_attention_prefill_tc5_bf16: %lld work items in one call", total);
+  const long long resident = 2ll * sm_count();
+  const int grid = (int)(total < resident ? total : resident);
   kern<<<grid, fg_tc5::THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                         out_stride, block_table, table_width, page_size, n_pages, pos, tile_req,
-                                        tile_tok0, tile_ntok, n_tiles, group, hpb, window,
-                                        scale * 1.4426950408889634f, status);
+                                        tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
+                                        scale * 1.4426950408889634f, work_counter, status);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
   return 0;
 }

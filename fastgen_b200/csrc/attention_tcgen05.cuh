@@ -73,8 +73,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ block_table,
                              int table_width, int page_size, int n_pages, const int* __restrict__ pos,
                              const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
-                             const int* __restrict__ tile_ntok, int n_tiles_total, int group,
-                             int heads_per_block, int window, float scale_log2, int* status) {
+                             const int* __restrict__ tile_ntok, int n_tiles_total, int n_kv_heads, int group,
+                             int heads_per_block, int window, float scale_log2, unsigned int* work_counter,
+                             int* status) {
   static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
   constexpr int HALVES = HD / 64;
   constexpr int STAGE_BYTES = HALVES * KV_HALF;
@@ -87,42 +88,24 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   unsigned char* Ks = Qs + HALVES * Q_HALF;         // [2][HALVES][64 rows][128 B]
   unsigned char* Vs = Ks + 2 * STAGE_BYTES;
   // full_k/full_v: a tile's keys/values have landed; s_done: its scores are in TMEM;
-  // p_ready: all 128 softmax threads stored its probabilities; o_done: its P V is done
+  // p_ready: all 128 softmax threads stored its probabilities; o_done: its P V is done.
+  // Every barrier completes once a key tile, and the block counts its key tiles through
+  // all the work it takes (`base` below): stage and parity follow that running number.
   __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int first_pos_s;
+  __shared__ unsigned int work_s;
   constexpr int PAGE_STAGE = 256;
   __shared__ int box_pages[PAGE_STAGE];
 
-  // The tile list is in ascending order of work and blockIdx.x runs fastest: all key/value
-  // heads of the heaviest tile start first, the lightest tiles fill the tail of the launch.
-  const int tile = n_tiles_total - 1 - blockIdx.y;
-  const int g = blockIdx.x, sub = blockIdx.z;
-  const int b = tile_req[tile];
-  const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (b < 0) return;
   const bool softmax_thread = tid < SOFTMAX_THREADS;
 
-  auto row_token = [&](int r) { return r / heads_per_block; };
-  auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
-  auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
-
-  bool my_valid = false;
-  int my_pos = -1;
-  if (softmax_thread) {
-    my_valid = row_valid(tid);
-    my_pos = my_valid ? pos[tok0 + row_token(tid)] : -1;
-    if (tid == 0) first_pos_s = my_pos;
-    // queries -> shared memory in the K-major operand layout (16-byte pieces, swizzled)
-    const __nv_bfloat16* src = q + (size_t)(tok0 + row_token(tid)) * q_stride + (g * group + row_head(tid)) * HD;
-#pragma unroll
-    for (int c = 0; c < HD / 8; ++c) {
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (my_valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-      *reinterpret_cast<uint4*>(Qs + (c / 8) * Q_HALF + fg_tma::swz(tid, c % 8)) = v;
-    }
-    fence_async_smem();  // written by ordinary stores, read by the tensor core
+  // Tensor memory first: while a block holds the allocation permit no other block of the
+  // kernel starts on its SM.
+  if (warp == LOAD_WARP) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
   }
   if (tid == SOFTMAX_THREADS) {
     mbar_init(&full_k[0], 1);
@@ -140,276 +123,335 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     mbar_init(&o_done[1], 1);
     mbar_fence_init();
   }
-  if (warp == 0) {
-    tmem_alloc(&tmem_base_s, TMEM_COLS);
-    tmem_relinquish();
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
 
-  const int min_pos = first_pos_s;  // tokens of a tile are consecutive positions
-  const int max_pos = min_pos + ntok - 1;
-  const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
-  const int k_lo = k_begin / KEYS * KEYS;
-  const int k_end = max_pos + 1;
-  const int n_tiles = (k_end - k_lo + KEYS - 1) / KEYS;
+  // Work = (query tile, key/value head, slice of the group's heads).  The blocks of the
+  // launch (two an SM) take the first items by their index and draw the rest from a
+  // counter: a block that started a new tile list entry only when another block of the
+  // launch had ended would wait for its SM to drain.  The list is in ascending order of
+  // work and is handed out from its end with the heads running fastest, so the longest
+  // items start first and the short ones fill the tail.
+  const unsigned int n_subs = (group + heads_per_block - 1) / heads_per_block;
+  const unsigned int total_work = (unsigned int)n_tiles_total * n_kv_heads * n_subs;
+  const unsigned int last_draw = (total_work > gridDim.x ? total_work - gridDim.x : 0u) + gridDim.x - 1;
+  int base = 0;  // key tiles this block has been through before the current item
 
-  if (warp == LOAD_WARP) {
-    // ================================ load warp ================================
-    // Keys and values of tile t go to stage t & 1 as soon as that stage is free: the
-    // keys' once S_{t-2} is done, the values' once O_{t-2} is.
-    const int* table_row = block_table + (size_t)b * table_width;
-    const int box_rows = min(page_size, KEYS);
-    const int n_boxes = KEYS / box_rows;
-    const int tiles_per_fill = PAGE_STAGE / n_boxes;
-    // page ids of a stretch of key tiles, looked up by the warp's 32 lanes
-    auto fill_pages = [&](int t_first) {
-      const int n = min(tiles_per_fill, n_tiles - t_first) * n_boxes;
-      for (int x = lane; x < n; x += 32) {
-        const int j0 = k_lo + t_first * KEYS + x * box_rows;
-        int page = -1;
-        if (j0 < k_end && j0 + box_rows > k_begin) {
-          const int logical = j0 / page_size;
-          page = logical < table_width ? table_row[logical] : -1;
-          if (page < 0 || page >= n_pages) {
-            if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
-            page = -1;
+  for (unsigned int work = blockIdx.x; work < total_work;) {
+    const int g = work % n_kv_heads;
+    const int tile = n_tiles_total - 1 - (int)((work / n_kv_heads) % n_tiles_total);
+    const int sub = work / n_kv_heads / n_tiles_total;
+    const int b = tile_req[tile];
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+    int n_tiles = 0;
+
+    if (b >= 0) {  // (uniform over the block)
+      auto row_token = [&](int r) { return r / heads_per_block; };
+      auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
+      auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
+
+      bool my_valid = false;
+      int my_pos = -1;
+      if (softmax_thread) {
+        my_valid = row_valid(tid);
+        my_pos = my_valid ? pos[tok0 + row_token(tid)] : -1;
+        if (tid == 0) first_pos_s = my_pos;
+        // queries -> shared memory in the K-major operand layout (16-byte pieces, swizzled)
+        const __nv_bfloat16* src =
+            q + (size_t)(tok0 + row_token(tid)) * q_stride + (g * group + row_head(tid)) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) {
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (my_valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+          *reinterpret_cast<uint4*>(Qs + (c / 8) * Q_HALF + fg_tma::swz(tid, c % 8)) = v;
+        }
+        fence_async_smem();  // written by ordinary stores, read by the tensor core
+      }
+      __syncthreads();
+
+      const int min_pos = first_pos_s;  // tokens of a tile are consecutive positions
+      const int max_pos = min_pos + ntok - 1;
+      const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
+      const int k_lo = k_begin / KEYS * KEYS;
+      const int k_end = max_pos + 1;
+      n_tiles = (k_end - k_lo + KEYS - 1) / KEYS;
+
+      if (warp == LOAD_WARP) {
+        // ================================ load warp ================================
+        // Keys and values of tile t go to the stage of its running number as soon as that
+        // stage is free: the keys' once the S two tiles back is done, the values' once
+        // that tile's O is.
+        const int* table_row = block_table + (size_t)b * table_width;
+        const int box_rows = min(page_size, KEYS);
+        const int n_boxes = KEYS / box_rows;
+        const int tiles_per_fill = PAGE_STAGE / n_boxes;
+        // page ids of a stretch of key tiles, looked up by the warp's 32 lanes
+        auto fill_pages = [&](int t_first) {
+          const int n = min(tiles_per_fill, n_tiles - t_first) * n_boxes;
+          for (int x = lane; x < n; x += 32) {
+            const int j0 = k_lo + t_first * KEYS + x * box_rows;
+            int page = -1;
+            if (j0 < k_end && j0 + box_rows > k_begin) {
+              const int logical = j0 / page_size;
+              page = logical < table_width ? table_row[logical] : -1;
+              if (page < 0 || page >= n_pages) {
+                if (status) atomicOr(status, FG_STATUS_BAD_PAGE);
+                page = -1;
+              }
+            }
+            box_pages[x] = page;
           }
-        }
-        box_pages[x] = page;
-      }
-      __syncwarp();
-    };
-    // bring tile t's keys (or values) into stage t & 1; boxes that hold no position of
-    // the request are zero-filled instead (a masked probability times garbage could be NaN)
-    auto load_tile = [&](int t, const int* pages, bool values) {
-      const int stage = t & 1;
-      unsigned char* base = (values ? Vs : Ks) + stage * STAGE_BYTES;
-      uint64_t* bar = values ? &full_v[stage] : &full_k[stage];
-      int n_valid = 0;
-      for (int i = 0; i < n_boxes; ++i) n_valid += pages[i] >= 0;
-      if (n_valid < n_boxes) {
-        for (int i = 0; i < n_boxes; ++i) {
-          if (pages[i] >= 0) continue;
-          const uint4 z = make_uint4(0, 0, 0, 0);
-          for (int h = 0; h < HALVES; ++h)
-            for (int c = lane; c < box_rows * 8; c += 32)
-              *reinterpret_cast<uint4*>(base + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
-        }
-        fence_async_smem();
-        __syncwarp();
-      }
-      if (lane == 0) {
-        mbar_arrive_expect(bar, n_valid * box_rows * HD * 2);
-        const int slot = (k_lo + t * KEYS) & (page_size - 1) & ~(KEYS - 1);  // 0 unless pages are longer than a tile
-        for (int i = 0; i < n_boxes; ++i) {
-          const int page = pages[i];
-          if (page < 0) continue;
-#pragma unroll
-          for (int h = 0; h < HALVES; ++h)
-            tma_load_5d(base + h * KV_HALF + i * box_rows * 128, values ? &v_map : &k_map, h * 64, slot, g, page,
-                        layer, bar);
-        }
-      }
-      __syncwarp();
-    };
-    int staged = 0;  // tiles of the staged stretch that were loaded
-    if (n_boxes == 1) {
-      // pages at least as long as a tile: one box a tile, and one lane does everything
-      // between the page look-ups (a single thread's instruction stream is what bounds
-      // this warp, so the loop is kept short)
-      const uint32_t k_bytes = KEYS * HD * 2;
-      for (int t = 0; t < n_tiles; ++t) {
-        if (staged == 0) fill_pages(t);
-        const int page = box_pages[staged];
-        const int stage = t & 1;
-        if (page >= 0) {
+          __syncwarp();
+        };
+        // bring tile t's keys (or values) into its stage; boxes that hold no position of
+        // the request are zero-filled instead (a masked probability times garbage could be NaN)
+        auto load_tile = [&](int t, const int* pages, bool values) {
+          const int stage = (base + t) & 1;
+          unsigned char* dst = (values ? Vs : Ks) + stage * STAGE_BYTES;
+          uint64_t* bar = values ? &full_v[stage] : &full_k[stage];
+          int n_valid = 0;
+          for (int i = 0; i < n_boxes; ++i) n_valid += pages[i] >= 0;
+          if (n_valid < n_boxes) {
+            for (int i = 0; i < n_boxes; ++i) {
+              if (pages[i] >= 0) continue;
+              const uint4 z = make_uint4(0, 0, 0, 0);
+              for (int h = 0; h < HALVES; ++h)
+                for (int c = lane; c < box_rows * 8; c += 32)
+                  *reinterpret_cast<uint4*>(dst + h * KV_HALF + i * box_rows * 128 + c * 16) = z;
+            }
+            fence_async_smem();
+            __syncwarp();
+          }
           if (lane == 0) {
-            const int slot = (k_lo + t * KEYS) & (page_size - 1);
-            unsigned char* kb = Ks + stage * STAGE_BYTES;
-            unsigned char* vb = Vs + stage * STAGE_BYTES;
-            if (t >= 2) mbar_wait(&s_done[stage], ((t - 2) >> 1) & 1, status);
-            mbar_arrive_expect(&full_k[stage], k_bytes);
+            mbar_arrive_expect(bar, n_valid * box_rows * HD * 2);
+            const int slot = (k_lo + t * KEYS) & (page_size - 1) & ~(KEYS - 1);  // 0 unless pages are longer than a tile
+            for (int i = 0; i < n_boxes; ++i) {
+              const int page = pages[i];
+              if (page < 0) continue;
 #pragma unroll
-            for (int h = 0; h < HALVES; ++h)
-              tma_load_5d(kb + h * KV_HALF, &k_map, h * 64, slot, g, page, layer, &full_k[stage]);
-            if (t >= 2) mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1, status);
-            mbar_arrive_expect(&full_v[stage], k_bytes);
+              for (int h = 0; h < HALVES; ++h)
+                tma_load_5d(dst + h * KV_HALF + i * box_rows * 128, values ? &v_map : &k_map, h * 64, slot, g,
+                            page, layer, bar);
+            }
+          }
+          __syncwarp();
+        };
+        int staged = 0;  // tiles of the staged stretch that were loaded
+        if (n_boxes == 1) {
+          // pages at least as long as a tile: one box a tile, and one lane does everything
+          // between the page look-ups (a single thread's instruction stream is what bounds
+          // this warp, so the loop is kept short)
+          const uint32_t k_bytes = KEYS * HD * 2;
+          for (int t = 0; t < n_tiles; ++t) {
+            if (staged == 0) fill_pages(t);
+            const int page = box_pages[staged];
+            const int gt = base + t, stage = gt & 1;
+            if (page >= 0) {
+              if (lane == 0) {
+                const int slot = (k_lo + t * KEYS) & (page_size - 1);
+                unsigned char* kb = Ks + stage * STAGE_BYTES;
+                unsigned char* vb = Vs + stage * STAGE_BYTES;
+                if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status);
+                mbar_arrive_expect(&full_k[stage], k_bytes);
 #pragma unroll
-            for (int h = 0; h < HALVES; ++h)
-              tma_load_5d(vb + h * KV_HALF, &v_map, h * 64, slot, g, page, layer, &full_v[stage]);
+                for (int h = 0; h < HALVES; ++h)
+                  tma_load_5d(kb + h * KV_HALF, &k_map, h * 64, slot, g, page, layer, &full_k[stage]);
+                if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status);
+                mbar_arrive_expect(&full_v[stage], k_bytes);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h)
+                  tma_load_5d(vb + h * KV_HALF, &v_map, h * 64, slot, g, page, layer, &full_v[stage]);
+              }
+            } else {
+              if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status);
+              load_tile(t, box_pages + staged, false);
+              if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status);
+              load_tile(t, box_pages + staged, true);
+            }
+            if (++staged == tiles_per_fill) staged = 0;
+            __syncwarp();  // the lanes stay together (the staged pages are replaced by all of them)
           }
         } else {
-          if (t >= 2) mbar_wait(&s_done[stage], ((t - 2) >> 1) & 1, status);
-          load_tile(t, box_pages + staged, false);
-          if (t >= 2) mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1, status);
-          load_tile(t, box_pages + staged, true);
+          for (int t = 0; t < n_tiles; ++t) {
+            if (staged == 0) fill_pages(t);
+            const int* pages = box_pages + staged * n_boxes;
+            const int gt = base + t, stage = gt & 1;
+            if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status);
+            load_tile(t, pages, false);
+            if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status);
+            load_tile(t, pages, true);
+            if (++staged == tiles_per_fill) staged = 0;
+          }
         }
-        if (++staged == tiles_per_fill) staged = 0;
-        __syncwarp();  // the lanes stay together (the staged pages are replaced by all of them)
-      }
-    } else {
-      for (int t = 0; t < n_tiles; ++t) {
-        if (staged == 0) fill_pages(t);
-        const int* pages = box_pages + staged * n_boxes;
-        if (t >= 2) mbar_wait(&s_done[t & 1], ((t - 2) >> 1) & 1, status);
-        load_tile(t, pages, false);
-        if (t >= 2) mbar_wait(&o_done[t & 1], ((t - 2) >> 1) & 1, status);
-        load_tile(t, pages, true);
-        if (++staged == tiles_per_fill) staged = 0;
-      }
-    }
-  } else if (warp == MMA_WARP) {
-    // ================================ MMA warp ================================
-    // One thread issues everything; products run in the order of issue, so S_{t+1}
-    // (which overwrites the columns of S_{t-1} / P_{t-1}) follows O_{t-1} by itself.
-    if (lane == 0) {
-      const uint64_t q_desc = smem_desc(Qs, 16), k_desc = smem_desc(Ks, 16), v_desc = smem_desc(Vs, KV_HALF);
-      auto issue_s = [&](int t) {
-        const int stage = t & 1;
-        mbar_wait(&full_k[stage], (t >> 1) & 1, status);
-        tc_fence_after();
-        const uint64_t kd = k_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
+      } else if (warp == MMA_WARP) {
+        // ================================ MMA warp ================================
+        // One thread issues everything; products run in the order of issue, so the S
+        // that overwrites the columns of the S / P two tiles back follows that tile's O
+        // by itself.
+        if (lane == 0) {
+          const uint64_t q_desc = smem_desc(Qs, 16), k_desc = smem_desc(Ks, 16), v_desc = smem_desc(Vs, KV_HALF);
+          auto issue_s = [&](int t) {
+            const int gt = base + t, stage = gt & 1;
+            mbar_wait(&full_k[stage], (gt >> 1) & 1, status);
+            tc_fence_after();
+            const uint64_t kd = k_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16(tmem + COL_S0 + stage * KEYS, q_desc + (uint64_t)(((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4),
-                   kd + (uint64_t)(((kk / 4) * KV_HALF + (kk % 4) * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
-        umma_commit(&s_done[stage]);
-      };
-      issue_s(0);
-      for (int t = 0; t < n_tiles; ++t) {
-        const int stage = t & 1;
-        if (t + 1 < n_tiles) issue_s(t + 1);
-        // all softmax threads have stored P_t (and rescaled O where needed)
-        mbar_wait(&p_ready[stage], (t >> 1) & 1, status);
-        mbar_wait(&full_v[stage], (t >> 1) & 1, status);
-        tc_fence_after();
-        const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
+            for (int kk = 0; kk < HD / 16; ++kk)
+              umma_f16(tmem + COL_S0 + stage * KEYS, q_desc + (uint64_t)(((kk / 4) * Q_HALF + (kk % 4) * 32) >> 4),
+                       kd + (uint64_t)(((kk / 4) * KV_HALF + (kk % 4) * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
+            umma_commit(&s_done[stage]);
+          };
+          issue_s(0);
+          for (int t = 0; t < n_tiles; ++t) {
+            const int gt = base + t, stage = gt & 1;
+            if (t + 1 < n_tiles) issue_s(t + 1);
+            // all softmax threads have stored P_t (and rescaled O where needed)
+            mbar_wait(&p_ready[stage], (gt >> 1) & 1, status);
+            mbar_wait(&full_v[stage], (gt >> 1) & 1, status);
+            tc_fence_after();
+            const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int j = 0; j < KEYS / 16; ++j)
-          umma_f16_ts(tmem + COL_O, tmem + COL_S0 + stage * KEYS + j * 8, vd + (uint64_t)((j * 16 * 128) >> 4),
-                      IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
-        umma_commit(&o_done[stage]);
-      }
-    }
-    __syncwarp();
-  } else {
-    // =============================== softmax warps ===============================
-    const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
-    float m_ref = -INFINITY, l_run = 0.f;
-    const float c = scale_log2;
-    const bool warp_full = __all_sync(0xffffffffu, my_valid);
-    int warp_max = my_pos, warp_min = my_valid ? my_pos : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, o));
-      warp_min = min(warp_min, __shfl_xor_sync(0xffffffffu, warp_min, o));
-    }
-    for (int t = 0; t < n_tiles; ++t) {
-      const int stage = t & 1;
-      const uint32_t s_addr = tmem + my_lane + COL_S0 + stage * KEYS;
-      mbar_wait(&s_done[stage], (t >> 1) & 1, status);
-      tc_fence_after();
-      const int k0 = k_lo + t * KEYS;
-      float s[KEYS];
-      tmem_ld64(s_addr, s);
-      const bool need_mask = !warp_full || k0 + KEYS - 1 > warp_min || (window > 0 && k0 <= warp_max - window);
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < KEYS; ++i) {
-          const int j = k0 + i;
-          const bool vis = my_pos >= 0 && j <= my_pos && (window <= 0 || j > my_pos - window);
-          if (!vis) s[i] = -INFINITY;
+            for (int j = 0; j < KEYS / 16; ++j)
+              umma_f16_ts(tmem + COL_O, tmem + COL_S0 + stage * KEYS + j * 8, vd + (uint64_t)((j * 16 * 128) >> 4),
+                          IDESC_O, (t > 0 || j > 0) ? 1u : 0u);
+            umma_commit(&o_done[stage]);
+          }
         }
-      }
-      // four independent chains for the maximum (and below for the sum): a row is one
-      // thread's, and a single chain of 64 dependent operations would be all latency
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int i = 0; i < KEYS; i += 8) {
-        mx4[0] = max3(mx4[0], s[i], s[i + 1]);
-        mx4[1] = max3(mx4[1], s[i + 2], s[i + 3]);
-        mx4[2] = max3(mx4[2], s[i + 4], s[i + 5]);
-        mx4[3] = max3(mx4[3], s[i + 6], s[i + 7]);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // raise the reference maximum only when it pays (or when there is none yet)
-      float alpha = 1.f;
-      bool raise = false;
-      if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * c > RESCALE_THRESHOLD)) {
-        raise = true;
-        alpha = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * c);
-        m_ref = mx;
-      }
-      float sum = 0.f;
-      uint32_t packed[KEYS / 2];
-      if (m_ref == -INFINITY) {
-#pragma unroll
-        for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
+        __syncwarp();
       } else {
-        const float mc = m_ref * c;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // =============================== softmax warps ===============================
+        const uint32_t my_lane = (uint32_t)(warp * 32) << 16;  // this warp's quarter of the TMEM lanes
+        float m_ref = -INFINITY, l_run = 0.f;
+        const float c = scale_log2;
+        const bool warp_full = __all_sync(0xffffffffu, my_valid);
+        int warp_max = my_pos, warp_min = my_valid ? my_pos : 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < KEYS; i += 4) {
-          const float p0 = ex2_approx(fmaf(s[i], c, -mc)), p1 = ex2_approx(fmaf(s[i + 1], c, -mc));
-          const float p2 = ex2_approx(fmaf(s[i + 2], c, -mc)), p3 = ex2_approx(fmaf(s[i + 3], c, -mc));
-          sum4[0] += p0;
-          sum4[1] += p1;
-          sum4[2] += p2;
-          sum4[3] += p3;
-          packed[i / 2] = pack_bf16(p0, p1);
-          packed[i / 2 + 1] = pack_bf16(p2, p3);
+        for (int o = 16; o > 0; o >>= 1) {
+          warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, o));
+          warp_min = min(warp_min, __shfl_xor_sync(0xffffffffu, warp_min, o));
         }
-        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      }
-      l_run = l_run * alpha + sum;
-      // P_t over the first 32 columns of S_t (this thread has read all of its row)
-      tmem_st32_raw(s_addr, packed);
-      // O_{t-1} is complete after this wait; O is then rescaled where a row's reference
-      // maximum was raised (warp-uniform decision).  (The barrier of this parity completes
-      // next for O_{t+1}, which needs this thread's P_{t+1}: the wait cannot fall behind.)
-      if (t > 0) mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1, status);
-      if (t > 0 && __any_sync(0xffffffffu, raise)) {
+        for (int t = 0; t < n_tiles; ++t) {
+          const int gt = base + t, stage = gt & 1;
+          const uint32_t s_addr = tmem + my_lane + COL_S0 + stage * KEYS;
+          mbar_wait(&s_done[stage], (gt >> 1) & 1, status);
+          tc_fence_after();
+          const int k0 = k_lo + t * KEYS;
+          float s[KEYS];
+          tmem_ld64(s_addr, s);
+          const bool need_mask =
+              !warp_full || k0 + KEYS - 1 > warp_min || (window > 0 && k0 <= warp_max - window);
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < KEYS; ++i) {
+              const int j = k0 + i;
+              const bool vis = my_pos >= 0 && j <= my_pos && (window <= 0 || j > my_pos - window);
+              if (!vis) s[i] = -INFINITY;
+            }
+          }
+          // four independent chains for the maximum (and below for the sum): a row is one
+          // thread's, and a single chain of 64 dependent operations would be all latency
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int i = 0; i < KEYS; i += 8) {
+            mx4[0] = max3(mx4[0], s[i], s[i + 1]);
+            mx4[1] = max3(mx4[1], s[i + 2], s[i + 3]);
+            mx4[2] = max3(mx4[2], s[i + 4], s[i + 5]);
+            mx4[3] = max3(mx4[3], s[i + 6], s[i + 7]);
+          }
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          // raise the reference maximum only when it pays (or when there is none yet)
+          float alpha = 1.f;
+          bool raise = false;
+          if (mx != -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * c > RESCALE_THRESHOLD)) {
+            raise = true;
+            alpha = (m_ref == -INFINITY) ? 0.f : exp2f((m_ref - mx) * c);
+            m_ref = mx;
+          }
+          float sum = 0.f;
+          uint32_t packed[KEYS / 2];
+          if (m_ref == -INFINITY) {
+#pragma unroll
+            for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
+          } else {
+            const float mc = m_ref * c;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < KEYS; i += 4) {
+              const float p0 = ex2_approx(fmaf(s[i], c, -mc)), p1 = ex2_approx(fmaf(s[i + 1], c, -mc));
+              const float p2 = ex2_approx(fmaf(s[i + 2], c, -mc)), p3 = ex2_approx(fmaf(s[i + 3], c, -mc));
+              sum4[0] += p0;
+              sum4[1] += p1;
+              sum4[2] += p2;
+              sum4[3] += p3;
+              packed[i / 2] = pack_bf16(p0, p1);
+              packed[i / 2 + 1] = pack_bf16(p2, p3);
+            }
+            sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+          }
+          l_run = l_run * alpha + sum;
+          // P_t over the first 32 columns of S_t (this thread has read all of its row)
+          tmem_st32_raw(s_addr, packed);
+          // O_{t-1} is complete after this wait; O is then rescaled where a row's reference
+          // maximum was raised (warp-uniform decision).  (The barrier of this parity completes
+          // next for O_{t+1}, which needs this thread's P_{t+1}: the wait cannot fall behind.)
+          if (t > 0) mbar_wait(&o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1, status);
+          if (t > 0 && __any_sync(0xffffffffu, raise)) {
+            tc_fence_after();
+#pragma unroll
+            for (int cc = 0; cc < HD / 32; ++cc) {
+              float part[32];
+              tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) part[i] *= alpha;
+              tmem_st32(tmem + my_lane + COL_O + cc * 32, part);
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&p_ready[stage]);
+        }
+        // ---- O / l -> out ----
+        const int gl = base + n_tiles - 1;
+        mbar_wait(&o_done[gl & 1], (gl >> 1) & 1, status);
         tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst =
+            out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;
 #pragma unroll
         for (int cc = 0; cc < HD / 32; ++cc) {
           float part[32];
           tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
+          if (my_valid) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) part[i] *= alpha;
-          tmem_st32(tmem + my_lane + COL_O + cc * 32, part);
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16(part[i] * inv, part[i + 1] * inv);
+              v.y = pack_bf16(part[i + 2] * inv, part[i + 3] * inv);
+              v.z = pack_bf16(part[i + 4] * inv, part[i + 5] * inv);
+              v.w = pack_bf16(part[i + 6] * inv, part[i + 7] * inv);
+              *reinterpret_cast<uint4*>(dst + cc * 32 + i) = v;
+            }
+          }
         }
-      }
-      tc_fence_before();
-      mbar_arrive(&p_ready[stage]);
-    }
-    // ---- O / l -> out ----
-    mbar_wait(&o_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, status);
-    tc_fence_after();
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* dst = out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;
-#pragma unroll
-    for (int cc = 0; cc < HD / 32; ++cc) {
-      float part[32];
-      tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
-      if (my_valid) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 v;
-          v.x = pack_bf16(part[i] * inv, part[i + 1] * inv);
-          v.y = pack_bf16(part[i + 2] * inv, part[i + 3] * inv);
-          v.z = pack_bf16(part[i + 4] * inv, part[i + 5] * inv);
-          v.w = pack_bf16(part[i + 6] * inv, part[i + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + cc * 32 + i) = v;
-        }
+        tc_fence_before();
       }
     }
+    base += n_tiles;
+    // The softmax warps leave an item last (its O is complete then, so every product that
+    // read Q or a stage of K/V has run); after this barrier Q and the page list are free.
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned int draw = atomicAdd(work_counter, 1u);
+      work_s = gridDim.x + draw;
+      if (draw == last_draw) *work_counter = 0u;  // the launch's last draw: ready for the next launch
+    }
+    __syncthreads();
+    work = work_s;
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == LOAD_WARP) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace fg_tc5

@@ -64,7 +64,7 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _P, _P],
+                                      _I, _F, _P, _P, _P],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P],
     "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
@@ -185,6 +185,8 @@ class Ops:
         self._scratch = {}
         self._stream_scratch = None
         self._stream_counters = None
+        # the prompt attention kernel's blocks draw their work from it; zero between launches
+        self._work_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
         # FG_STREAM_GEMM: "all" uses the tcgen05 weight-streaming product for every product of
         # 9..256 tokens, "auto" where it measured faster than the library, default: never
@@ -439,14 +441,15 @@ class Ops:
         if tiles.n and use_tma:
             # head sizes 64 and 128: tcgen05.mma with S and O in tensor memory; other
             # multiples of 64: mma.sync on the same TMA tiles (FG_NO_TCGEN05=1 forces that)
-            fn = (lib.fg_attention_prefill_tc5_bf16 if head_dim in (64, 128) and self.use_tcgen05
-                  else lib.fg_attention_prefill_tma_bf16)
-            _check(lib, fn(
-                _ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[2].ptr,
-                memory.tensor_maps[3].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
-                page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
-                _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
-                _ptr(self.status), _stream()))
+            args = (_ptr(q), q.stride(0), _ptr(out), out.stride(0), memory.tensor_maps[2].ptr,
+                    memory.tensor_maps[3].ptr, memory.layer_index, _ptr(block_table), block_table.shape[1],
+                    page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
+                    _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale))
+            if head_dim in (64, 128) and self.use_tcgen05:
+                _check(lib, lib.fg_attention_prefill_tc5_bf16(
+                    *args, _ptr(self._work_counter), _ptr(self.status), _stream()))
+            else:
+                _check(lib, lib.fg_attention_prefill_tma_bf16(*args, _ptr(self.status), _stream()))
         elif tiles.n:
             _check(lib, lib.fg_attention_prefill_bf16(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), *common,
