@@ -355,6 +355,9 @@ CASES = [
       (333, 1), (40, 30)], 16, 8, 128, 16, 300),
     ([(1500 + 37 * i, 1) for i in range(10)] + [(3 + 129 * i, 1) for i in range(10)], 20, 2, 64, 8, None),
     ([(1500, 1), (255, 1), (256, 1), (1023, 1), (1024, 1), (700, 1), (1, 1), (1300, 1)], 8, 8, 128, 256, None),
+    # more (query tile, head) items than resident blocks: blocks of the prompt kernel take several items,
+    # with odd and even numbers of key tiles each (the stages of their rings change sides between items)
+    ([(37, 2600), (5, 1), (0, 70)], 16, 16, 64, 16, None),
 ]
 
 
