@@ -70,7 +70,7 @@ _ATTN_SIGNATURES = {
     "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
 }
 
-SKINNY_MAX_M = 8      # most tokens the weight-streaming product is used for (it takes up to 32)
+SKINNY_MAX_M = int(os.environ.get("FG_SKINNY_MAX_M", "8"))      # most tokens the weight-streaming product is used for (it takes up to 32)
 SIMT_ROWS = 16       # query rows per block of the float32 attention kernel
 PREFILL_ROWS = 64    # ... of the bfloat16 prompt kernel
 PREFILL_TMA_ROWS = 128  # ... of the bfloat16 prompt kernel with tiled TMA loads
