@@ -30,6 +30,7 @@ import torch
 
 from ..config import load_model_args, read_config
 from ..sampling import Sampler
+from ..utils.misc import hashints
 from .model import Model
 from .scheduler import Request, Scheduler
 from .step import Engine, StepEntry
@@ -268,6 +269,10 @@ class Fastgen:
             if not self.gen_args.use_sampling:
                 temp = 0.0
             self.scheduler.add(pkt.thread_id, pkt.tokens, temp, pkt.max_gen)
+            if logger.isEnabledFor(logging.DEBUG):
+                # the reference keeps this hash on every lane (generate.py:112)
+                logger.debug("request %s: %d prompt tokens, hash %d", pkt.thread_id, len(pkt.tokens),
+                             hashints(pkt.tokens))
             if len(self.scheduler.waiting) >= 2 * self.max_batch:
                 break
         return eoq
