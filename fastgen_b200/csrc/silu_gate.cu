@@ -39,7 +39,11 @@ silu_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __re
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+      // float32 throughout; the special-function unit's exponential and reciprocal (a few
+      // units in the last place of float32, far below the bfloat16 rounding that follows):
+      // with expf() and an IEEE division the kernel was bound by instruction issue
+      o2[k] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x,
+                                    __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
     }
     return o4;
   };
