@@ -1,6 +1,7 @@
 """Each kernel alone against a plain float64 reference, at sizes other than the engine's."""
 
 import math
+import os
 import random
 
 import numpy as np
@@ -252,6 +253,8 @@ def test_rope_kv_write(ops32, dtype, hq, hkv, hd, page):
         ops32.check_status()
 
 
+@pytest.mark.skipif(os.environ.get("FG_STREAM_GEMM", "off") == "off",
+                    reason="the tcgen05 weight-streaming product is opt-in (FG_STREAM_GEMM=auto|all) and so is its test")
 @pytest.mark.parametrize("m,n,k", [(16, 128, 64), (9, 4096, 4096), (33, 1000, 200), (64, 6144, 4096),
                                    (100, 28672, 4096), (64, 4096, 14336), (128, 331, 72), (256, 2048, 512)])
 def test_linear_stream(ops16, m, n, k):
