@@ -85,40 +85,47 @@ struct Ring {
   static constexpr size_t BYTES = (size_t)STAGES * PIECES * THREADS * 16;
 };
 
-template <int NT, typename TO, int EPI>
-__global__ void __launch_bounds__(THREADS)
-gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
-                   TO* __restrict__ y, int ldy, int M, int N, int K, QkvEpilogue qkv) {
-  constexpr int PIECES = Ring<NT>::PIECES;
-  constexpr int STAGES = Ring<NT>::STAGES;
-  extern __shared__ __align__(16) unsigned char ring_raw[];
-  uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [STAGES][PIECES][THREADS]
-  __shared__ float red[WARPS][ROWS][NT * 8];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n0 = blockIdx.x * ROWS;
-  const int r = lane >> 2, c = lane & 3;
-  // rows beyond N and tokens beyond M are zero-filled and discarded at the end
-  const bool row_a = n0 + r < N, row_b = n0 + r + 8 < N;
-  const __nv_bfloat16* wa = w + (size_t)(row_a ? n0 + r : 0) * ldw + c * 8;
-  const __nv_bfloat16* wb = w + (size_t)(row_b ? n0 + r + 8 : 0) * ldw + c * 8;
-  const __nv_bfloat16* xr[NT];
-  bool tok_ok[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int tok = nt * 8 + r;
-    tok_ok[nt] = tok < M;
-    xr[nt] = x + (size_t)(tok_ok[nt] ? tok : 0) * ldx + c * 8;
-  }
+// One block's product: 16 rows of W (from row n0) against the tokens' x.  The pieces a
+// thread streams, its ring and its accumulators; the callers decide when the weights'
+// first stages are issued (they may go ahead of data that is not ready yet).
+template <int NT>
+struct BlockProduct {
+  static constexpr int PIECES = Ring<NT>::PIECES;
+  static constexpr int STAGES = Ring<NT>::STAGES;
+  uint4* ring;  // [STAGES][PIECES][THREADS]
+  const __nv_bfloat16 *wa, *wb, *xr[NT];
+  bool row_a, row_b, tok_ok[NT];
   float acc[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  int K, my_chunks, tid, warp, r, c;
 
-  const int n_chunks = (K + CHUNK - 1) / CHUNK;
-  const int my_chunks = warp < n_chunks ? (n_chunks - warp + WARPS - 1) / WARPS : 0;
+  __device__ __forceinline__ void setup(uint4* ring_, const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw,
+                                        int M, int N, int K_, int n0) {
+    ring = ring_;
+    K = K_;
+    tid = threadIdx.x;
+    warp = tid >> 5;
+    const int lane = tid & 31;
+    r = lane >> 2;
+    c = lane & 3;
+    // rows beyond N and tokens beyond M are zero-filled and discarded at the end
+    row_a = n0 + r < N;
+    row_b = n0 + r + 8 < N;
+    wa = w + (size_t)(row_a ? n0 + r : 0) * ldw + c * 8;
+    wb = w + (size_t)(row_b ? n0 + r + 8 : 0) * ldw + c * 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + r;
+      tok_ok[nt] = tok < M;
+      xr[nt] = x + (size_t)(tok_ok[nt] ? tok : 0) * ldx + c * 8;
+      acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    }
+    const int n_chunks = (K + CHUNK - 1) / CHUNK;
+    my_chunks = warp < n_chunks ? (n_chunks - warp + WARPS - 1) / WARPS : 0;
+  }
 
   // issue the copies of this thread's i-th chunk into stage i % STAGES: the pieces of
   // W, the pieces of x, or both
-  auto issue = [&](int i, bool do_w, bool do_x) {
+  __device__ __forceinline__ void issue(int i, bool do_w, bool do_x) {
     uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
     const int k = (warp + i * WARPS) * CHUNK;
 #pragma unroll
@@ -135,7 +142,90 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
           cp_async_16<true>(slot + (4 + nt * 2 + h) * THREADS, xr[nt] + kk, ok && tok_ok[nt]);
       }
     }
-  };
+  }
+
+  // the weights of the first stages (they depend on nothing that is computed in the step)
+  __device__ __forceinline__ void first_weights() {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+      if (s < my_chunks) issue(s, true, false);
+  }
+
+  // the x pieces of the first stages, the main loop, and the warps' sums into `red`
+  __device__ __forceinline__ void run(float (*red)[ROWS][NT * 8]) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      if (s < my_chunks) issue(s, false, true);
+      cp_async_commit();
+    }
+    for (int i = 0; i < my_chunks; ++i) {
+      if (i + STAGES - 1 < my_chunks) issue(i + STAGES - 1, true, true);
+      cp_async_commit();
+      cp_async_wait<STAGES - 1>();  // this thread's copies of chunk i have landed; only it reads them
+      const uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 a_lo = slot[(2 * h) * THREADS], a_hi = slot[(2 * h + 1) * THREADS];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 b = slot[(4 + nt * 2 + h) * THREADS];
+          mma(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+          mma(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+        }
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      red[warp][r][nt * 8 + 2 * c] = acc[nt][0];
+      red[warp][r][nt * 8 + 2 * c + 1] = acc[nt][1];
+      red[warp][r + 8][nt * 8 + 2 * c] = acc[nt][2];
+      red[warp][r + 8][nt * 8 + 2 * c + 1] = acc[nt][3];
+    }
+    __syncthreads();
+  }
+};
+
+// the warps' partial sums of (row, token), in warp order
+template <int NT>
+__device__ __forceinline__ float block_total(float (*red)[ROWS][NT * 8], int row, int tok) {
+  float s = 0.f;
+#pragma unroll
+  for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][tok];
+  return s;
+}
+
+template <int NT, typename TO>
+__device__ __forceinline__ void epilogue_plain(float (*red)[ROWS][NT * 8], TO* y, int ldy, int M, int N, int n0) {
+  for (int i = threadIdx.x; i < ROWS * NT * 8; i += THREADS) {
+    const int tok = i / ROWS, row = i - tok * ROWS;  // consecutive threads write consecutive columns of y
+    if (tok < M && n0 + row < N) y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(block_total<NT>(red, row, tok));
+  }
+}
+
+// rows 0..7 are the gates and rows 8..15 the ups of features n0/2 .. n0/2+7
+template <int NT, typename TO>
+__device__ __forceinline__ void epilogue_swiglu(float (*red)[ROWS][NT * 8], TO* y, int ldy, int M, int N, int n0) {
+  for (int i = threadIdx.x; i < 8 * NT * 8; i += THREADS) {
+    const int tok = i / 8, f = i - tok * 8;
+    if (tok < M && n0 + 8 + f < N) {
+      const float g = block_total<NT>(red, f, tok), u = block_total<NT>(red, f + 8, tok);
+      // both are rounded to bfloat16 first, as a separate gate kernel would see them
+      const float gr = __bfloat162float(__float2bfloat16_rn(g)), ur = __bfloat162float(__float2bfloat16_rn(u));
+      y[(size_t)tok * ldy + n0 / 2 + f] = from_f32<TO>(gr / (1.f + expf(-gr)) * ur);
+    }
+  }
+}
+
+template <int NT, typename TO, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
+                   TO* __restrict__ y, int ldy, int M, int N, int K, QkvEpilogue qkv) {
+  extern __shared__ __align__(16) unsigned char ring_raw[];
+  __shared__ float red[WARPS][ROWS][NT * 8];
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * ROWS;
+  BlockProduct<NT> block;
+  block.setup(reinterpret_cast<uint4*>(ring_raw), x, ldx, w, ldw, M, N, K, n0);
 
   // The weights do not depend on the kernel before this one: their first stages are on
   // their way while that kernel finishes.  x (its output) is only touched after the wait.
@@ -171,67 +261,19 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
       }
     }
   }
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s)
-    if (s < my_chunks) issue(s, true, false);
+  block.first_weights();
   pdl_wait();
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < my_chunks) issue(s, false, true);
-    cp_async_commit();
-  }
-  for (int i = 0; i < my_chunks; ++i) {
-    if (i + STAGES - 1 < my_chunks) issue(i + STAGES - 1, true, true);
-    cp_async_commit();
-    cp_async_wait<STAGES - 1>();  // this thread's copies of chunk i have landed; only it reads them
-    const uint4* slot = ring + (size_t)(i % STAGES) * PIECES * THREADS + tid;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint4 a_lo = slot[(2 * h) * THREADS], a_hi = slot[(2 * h + 1) * THREADS];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const uint4 b = slot[(4 + nt * 2 + h) * THREADS];
-        mma(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-        mma(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
-      }
-    }
-  }
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    red[warp][r][nt * 8 + 2 * c] = acc[nt][0];
-    red[warp][r][nt * 8 + 2 * c + 1] = acc[nt][1];
-    red[warp][r + 8][nt * 8 + 2 * c] = acc[nt][2];
-    red[warp][r + 8][nt * 8 + 2 * c + 1] = acc[nt][3];
-  }
-  __syncthreads();
-  auto total = [&](int row, int tok) {
-    float s = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < WARPS; ++wi) s += red[wi][row][tok];
-    return s;
-  };
+  block.run(red);
   if (EPI == EPI_PLAIN) {
-    for (int i = tid; i < ROWS * NT * 8; i += THREADS) {
-      const int tok = i / ROWS, row = i - tok * ROWS;  // consecutive threads write consecutive columns of y
-      if (tok < M && n0 + row < N) y[(size_t)tok * ldy + n0 + row] = from_f32<TO>(total(row, tok));
-    }
+    epilogue_plain<NT, TO>(red, y, ldy, M, N, n0);
   } else if (EPI == EPI_SWIGLU) {
-    // rows 0..7 are the gates and rows 8..15 the ups of features n0/2 .. n0/2+7
-    for (int i = tid; i < 8 * NT * 8; i += THREADS) {
-      const int tok = i / 8, f = i - tok * 8;
-      if (tok < M && n0 + 8 + f < N) {
-        const float g = total(f, tok), u = total(f + 8, tok);
-        // both are rounded to bfloat16 first, as a separate gate kernel would see them
-        const float gr = __bfloat162float(__float2bfloat16_rn(g)), ur = __bfloat162float(__float2bfloat16_rn(u));
-        y[(size_t)tok * ldy + n0 / 2 + f] = from_f32<TO>(gr / (1.f + expf(-gr)) * ur);
-      }
-    }
+    epilogue_swiglu<NT, TO>(red, y, ldy, M, N, n0);
   } else {
     // the block's 16 rows are 8 adjacent pairs of one head of q, k or v; a thread's pair,
     // angle and destination were worked out before the main loop
     if (e_tok >= 0) {
       const int pr = (e_n - n0) >> 1;
-      float re = total(2 * pr, e_tok), im = total(2 * pr + 1, e_tok);
+      float re = block_total<NT>(red, 2 * pr, e_tok), im = block_total<NT>(red, 2 * pr + 1, e_tok);
       if (e_kind != 2) {
         // the product is rounded to bfloat16 before the rotation, as a separate kernel would see it
         re = __bfloat162float(__float2bfloat16_rn(re));

@@ -24,3 +24,30 @@ def test_against_the_xxhash_package():
         vals = [rng.randrange(0, 1 << 31) for _ in range(n)]
         digest = xxhash.xxh32_digest(np.array(vals, dtype=np.uint32).view(np.uint8))
         assert hashints(vals) == struct.unpack("<I", digest)[0] & 0x7FFFFFFF
+
+
+def test_every_declared_signature_belongs_to_its_library():
+    """A function called through ctypes without its argument types gets its pointers cut
+    to 32 bits: each table of signatures names functions of its own library only."""
+    import re
+    from pathlib import Path
+
+    from fastgen_b200.csrc import build, ops
+
+    csrc = Path(build.__file__).parent
+    def exported(files):
+        names = set()
+        for f in files:
+            names |= set(re.findall(r'extern "C" \w[\w\s\*]*?\b(fg_\w+)\(', (csrc / f).read_text()))
+        return names
+    core = exported(build.CORE_SOURCES)
+    attn = exported(["attention.cu"])
+    assert set(ops._CORE_SIGNATURES) <= core, set(ops._CORE_SIGNATURES) - core
+    assert set(ops._ATTN_SIGNATURES) <= attn, set(ops._ATTN_SIGNATURES) - attn
+    # and every exported function that takes a pointer is declared
+    called = set(re.findall(r"\blib\.(fg_\w+)\(", Path(ops.__file__).read_text()))
+    undeclared = called - set(ops._CORE_SIGNATURES) - set(ops._ATTN_SIGNATURES)
+    int_only = {"fg_attention_decode_scratch_floats", "fg_attention_decode_split", "fg_attention_prefill_rows",
+                "fg_attention_rows_per_block", "fg_gemm_stream_max_m", "fg_gemm_stream_scratch_floats",
+                "fg_last_error"}
+    assert undeclared <= int_only, undeclared - int_only
