@@ -105,7 +105,8 @@ def test_linear_bf16(ops16):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
-@pytest.mark.parametrize("n,k", [(320, 192), (331, 200), (4096, 4096), (1000, 14336), (17, 72), (64, 8)])
+@pytest.mark.parametrize("n,k", [(320, 192), (331, 200), (4096, 4096), (1000, 14336), (17, 72), (64, 8),
+                                 (20011, 136), (16000, 520)])  # the last two: blocks that walk many row blocks
 def test_gemm_skinny(ops16, request, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
@@ -131,7 +132,7 @@ def test_gemm_skinny(ops16, request, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 8, 11, 32])
-@pytest.mark.parametrize("f,k", [(512, 192), (328, 200), (14336, 4096), (8, 72)])
+@pytest.mark.parametrize("f,k", [(512, 192), (328, 200), (14336, 4096), (8, 72), (9000, 72)])
 def test_gemm_skinny_swiglu(ops16, m, f, k):
     """Gate/up product with the gate in its epilogue, against product-then-gate."""
     g = torch.Generator().manual_seed(m * k + f)
