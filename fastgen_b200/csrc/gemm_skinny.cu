@@ -25,8 +25,6 @@
 //
 // It stands where the reference calls F.linear on decode batches
 // (fastgen/forward.py:438-440,470,491-496,513); larger M goes to the library.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace {
@@ -293,131 +291,6 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
   }
 }
 
-// The same product for matrices of many more row blocks than the GPU holds blocks: a launch
-// of as many blocks as are resident at once, each walking every gridDim.x-th row block.  A
-// thread's copies run on through its row blocks (the ring never drains between them), so
-// only the launch's first loads are exposed, where a launch of one short block a row block
-// exposes every block's.  The warps' sums alternate between two buffers, so a row block
-// costs one block-wide barrier.  Arithmetic and order of a row block are those above.
-template <int NT, typename TO, int EPI>
-__global__ void __launch_bounds__(THREADS)
-gemm_skinny_walk_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
-                        TO* __restrict__ y, int ldy, int M, int N, int K) {
-  static_assert(EPI == EPI_PLAIN || EPI == EPI_SWIGLU, "plain and SwiGLU epilogues");
-  constexpr int PIECES = Ring<NT>::PIECES;
-  constexpr int STAGES = Ring<NT>::STAGES;
-  extern __shared__ __align__(16) unsigned char ring_raw[];
-  uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [STAGES][PIECES][THREADS]
-  __shared__ float red[2][WARPS][ROWS][NT * 8];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int r = lane >> 2, c = lane & 3;
-  const int units = (N + ROWS - 1) / ROWS;
-  const int my_units = (int)blockIdx.x < units ? (units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-  const int n_chunks = (K + CHUNK - 1) / CHUNK;
-  const int my_chunks = warp < n_chunks ? (n_chunks - warp + WARPS - 1) / WARPS : 0;  // a row block
-  const __nv_bfloat16* xr[NT];
-  bool tok_ok[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    const int tok = nt * 8 + r;
-    tok_ok[nt] = tok < M;
-    xr[nt] = x + (size_t)(tok_ok[nt] ? tok : 0) * ldx + c * 8;
-  }
-  auto unit_row = [&](int u) { return ((int)blockIdx.x + u * (int)gridDim.x) * ROWS; };
-  // the copies of chunk i of this block's u-th row block into a stage of the ring
-  auto issue = [&](int u, int i, int stage, bool do_w, bool do_x) {
-    uint4* slot = ring + (size_t)stage * PIECES * THREADS + tid;
-    const int n0 = unit_row(u);
-    const bool row_a = n0 + r < N, row_b = n0 + r + 8 < N;
-    const __nv_bfloat16* wa = w + (size_t)(row_a ? n0 + r : 0) * ldw + c * 8;
-    const __nv_bfloat16* wb = w + (size_t)(row_b ? n0 + r + 8 : 0) * ldw + c * 8;
-    const int k = (warp + i * WARPS) * CHUNK;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int kk = k + h * 32;
-      const bool ok = kk + c * 8 < K;
-      if (do_w) {
-        cp_async_16<false>(slot + (2 * h) * THREADS, wa + kk, ok && row_a);
-        cp_async_16<false>(slot + (2 * h + 1) * THREADS, wb + kk, ok && row_b);
-      }
-      if (do_x) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-          cp_async_16<true>(slot + (4 + nt * 2 + h) * THREADS, xr[nt] + kk, ok && tok_ok[nt]);
-      }
-    }
-  };
-  pdl_trigger();
-  // (row block, chunk) of the next copies and their stage; the first stages' weights go
-  // ahead of the wait for the kernel before this one, their x pieces after it
-  int iu = 0, ic = 0, is = 0;
-  auto advance = [&]() {
-    if (++ic == my_chunks) {
-      ic = 0;
-      ++iu;
-    }
-    if (++is == STAGES) is = 0;
-  };
-  const bool any = my_chunks > 0;
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s)
-    if (any && iu < my_units) {
-      issue(iu, ic, is, true, false);
-      advance();
-    }
-  pdl_wait();
-  iu = ic = is = 0;
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (any && iu < my_units) {
-      issue(iu, ic, is, false, true);
-      advance();
-    }
-    cp_async_commit();
-  }
-  int cs = 0;  // the stage to consume
-  for (int u = 0; u < my_units; ++u) {
-    float acc[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-    for (int i = 0; i < my_chunks; ++i) {
-      if (iu < my_units) {
-        issue(iu, ic, is, true, true);
-        advance();
-      }
-      cp_async_commit();
-      cp_async_wait<STAGES - 1>();  // this thread's copies of the chunk in turn have landed
-      const uint4* slot = ring + (size_t)cs * PIECES * THREADS + tid;
-      if (++cs == STAGES) cs = 0;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint4 a_lo = slot[(2 * h) * THREADS], a_hi = slot[(2 * h + 1) * THREADS];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint4 b = slot[(4 + nt * 2 + h) * THREADS];
-          mma(acc[nt], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-          mma(acc[nt], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
-        }
-      }
-    }
-    float (*sums)[ROWS][NT * 8] = red[u & 1];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      sums[warp][r][nt * 8 + 2 * c] = acc[nt][0];
-      sums[warp][r][nt * 8 + 2 * c + 1] = acc[nt][1];
-      sums[warp][r + 8][nt * 8 + 2 * c] = acc[nt][2];
-      sums[warp][r + 8][nt * 8 + 2 * c + 1] = acc[nt][3];
-    }
-    // The other buffer was last read in the row block before this one's epilogue, which
-    // every thread left before it came to this barrier.
-    __syncthreads();
-    if (EPI == EPI_PLAIN)
-      epilogue_plain<NT, TO>(sums, y, ldy, M, N, unit_row(u));
-    else
-      epilogue_swiglu<NT, TO>(sums, y, ldy, M, N, unit_row(u));
-  }
-}
-
 template <int NT, typename TO, int EPI>
 int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
                const QkvEpilogue& qkv, cudaStream_t stream) {
@@ -434,48 +307,9 @@ int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy,
   return 0;
 }
 
-// FG_SKINNY_WALK=0 in the environment keeps every product on the launch of one block a row block.
-bool walk_enabled() {
-  static const bool on = [] {
-    const char* v = getenv("FG_SKINNY_WALK");
-    return !(v != nullptr && v[0] == '0');
-  }();
-  return on;
-}
-
-// The walking launch, for matrices of more row blocks than `min_rounds` times the resident
-// blocks; returns false when the product should take the plain launch.
-template <int NT, typename TO, int EPI>
-bool launch_walk(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
-                 cudaStream_t stream) {
-  auto kern = gemm_skinny_walk_kernel<NT, TO, EPI>;
-  constexpr size_t smem = Ring<NT>::BYTES;
-  static int resident = -1;  // blocks the GPU holds at once (0: could not be found out)
-  if (resident < 0) {
-    resident = 0;
-    int dev = 0, sms = 0, per_sm = 0;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
-        cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem) == cudaSuccess)
-      resident = per_sm * sms;
-  }
-  const int units = (N + ROWS - 1) / ROWS;
-  if (!walk_enabled() || resident <= 0 || units < 3 * resident) return false;
-  // all resident blocks: launches of fewer blocks that share the row blocks out evenly
-  // (256 for the 1,792 of the 8B gate/up product) measured 1 to 2 % of a decode step slower
-  fg_launch_pdl(kern, dim3(resident), dim3(THREADS), smem, stream, (const __nv_bfloat16*)x, ldx,
-                (const __nv_bfloat16*)w, ldw, (TO*)y, ldy, M, N, K);
-  return true;
-}
-
 template <typename TO, int EPI>
 int launch(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
            const QkvEpilogue& qkv, cudaStream_t stream) {
-  if constexpr (EPI != EPI_QKV) {
-    // few tokens against a tall matrix (gate/up, the vocabulary): blocks that walk the rows
-    if (M <= 8 && launch_walk<1, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, stream)) return 0;
-  }
   if (M <= 8) return launch_one<1, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
   if (M <= 16) return launch_one<2, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
   return launch_one<4, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);

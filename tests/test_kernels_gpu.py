@@ -106,7 +106,7 @@ def test_linear_bf16(ops16):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("n,k", [(320, 192), (331, 200), (4096, 4096), (1000, 14336), (17, 72), (64, 8),
-                                 (20011, 136), (16000, 520)])  # the last two: blocks that walk many row blocks
+                                 (20011, 136), (16000, 520)])  # the last two: many more row blocks than the GPU holds blocks
 def test_gemm_skinny(ops16, request, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
@@ -488,37 +488,3 @@ def test_sampling_distribution(ops32):
     u = ops32.sample_uniform(99, keys, posn).cpu()
     assert abs(float(u.mean()) - 0.5) < 0.02 and abs(float(u.var()) - 1 / 12) < 0.01
 
-
-def test_walking_launch_gives_the_plain_launch_bit_for_bit(tmp_path):
-    """Tall matrices take blocks that walk the row blocks; a row block's arithmetic and order
-    are those of the launch of one block a row block (run once each, in processes of their own:
-    the choice is read from the environment when the library is first used)."""
-    import subprocess
-    import sys
-    from pathlib import Path
-
-    root = Path(__file__).resolve().parent.parent
-    script = (
-        "import sys, math, torch\n"
-        f"sys.path.insert(0, {str(root)!r})\n"
-        "from fastgen_b200.csrc.ops import Ops\n"
-        "ops = Ops(torch.bfloat16, 'cuda:0')\n"
-        "g = torch.Generator().manual_seed(11)\n"
-        "outs = []\n"
-        "for m, n, k in ((8, 20011, 136), (3, 16000, 520)):\n"
-        "    x = torch.randn(m, k, generator=g).to('cuda:0', torch.bfloat16)\n"
-        "    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to('cuda:0', torch.bfloat16)\n"
-        "    outs.append(ops.linear(x, w, out_dtype=torch.float32).cpu())\n"
-        "    outs.append(ops.linear_swiglu(x, w[: n // 16 * 16]).cpu())\n"
-        "ops.check_status()\n"
-        "torch.save(outs, sys.argv[1])\n"
-    )
-    results = []
-    for walk in ("0", "1"):
-        out = tmp_path / f"walk{walk}.pt"
-        env = dict(os.environ, FG_SKINNY_WALK=walk)
-        subprocess.run([sys.executable, "-c", script, str(out)], check=True, env=env, timeout=300)
-        results.append(torch.load(out))
-    assert len(results[0]) == 4
-    for a, b in zip(*results):
-        assert torch.equal(a, b)
