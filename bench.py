@@ -102,6 +102,20 @@ def model_flops(cfg: dict, n_layers: int, t: int, rows: int) -> float:
     return n_layers * (per_layer + attn) + 2 * rows * d * v
 
 
+def describe_config(cfg: dict, batch: int, context: int, layers: int, layers_full: int, first: int, last: int,
+                    peaks_source: str) -> dict:
+    """The sizes of the run, flat (the record keeps at most 20 keys of it, and no lists)."""
+    return {
+        "model": "Llama-3.1-8B shape", "global_batch": batch, "seq_len": context,
+        "parallelism": "single GPU", "layers": layers, "layers_full": layers_full,
+        "hidden": cfg["hidden_size"], "ffn": cfg["intermediate_size"], "q_heads": cfg["num_attention_heads"],
+        "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"],
+        "vocab": cfg["vocab_size"], "page": PAGE, "decode_from": first, "decode_to": last,
+        "prefill_tokens": PREFILL_TOKENS,
+        "l2": "inputs larger than L2 (all weights are streamed every step)", "peaks": peaks_source,
+    }
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -265,14 +279,8 @@ def run_ours(args) -> dict:
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights seed 4, uniform random token ids)",
         "impl": "ours",
-        "config": {
-            "model": "Llama-3.1-8B shape", "global_batch": args.batch, "seq_len": ctx_len,
-            "parallelism": "single GPU", "layers": n_layers, "layers_full": full_layers,
-            "hidden": cfg["hidden_size"], "ffn": cfg["intermediate_size"], "q_heads": cfg["num_attention_heads"],
-            "kv_heads": cfg["num_key_value_heads"], "head_dim": 128, "vocab": vocab, "page": PAGE,
-            "decode_from": main["first"], "decode_to": main["last"], "prefill_tokens": PREFILL_TOKENS,
-            "l2": "inputs larger than L2 (all weights are streamed every step)", "peaks": pk["source"],
-        },
+        "config": describe_config(cfg, args.batch, ctx_len, n_layers, full_layers, main["first"], main["last"],
+                                  pk["source"]),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(main["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(main["gbs"] / pk["hbm_gbs"], 4)},
