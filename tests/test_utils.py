@@ -51,3 +51,25 @@ def test_every_declared_signature_belongs_to_its_library():
                 "fg_attention_rows_per_block", "fg_gemm_stream_max_m", "fg_gemm_stream_scratch_floats",
                 "fg_last_error"}
     assert undeclared <= int_only, undeclared - int_only
+
+
+def test_attention_tiles_are_in_ascending_order_of_keys():
+    """The prompt kernels hand the tile list out from its end: the tiles that read the most
+    keys come last in it, whatever the order of the sequences in the batch."""
+    from fastgen_b200.engine.step import StepContext
+
+    ctx = StepContext("cpu")
+    # three sequences: 70 new tokens on 500 cached, one decoded token on 900, 130 new on none
+    ctx.host_seq_slot = [4, 1, 7]
+    ctx.host_seq_start = [0, 70, 71, 201]
+    ctx.host_seq_cached = [500, 900, 0]
+    tiles = ctx.attention_tiles(32, min_tokens=2)
+    req, tok0, ntok = tiles.req.tolist(), tiles.tok0.tolist(), tiles.ntok.tolist()
+    assert tiles.n == 3 + 5 and sorted(set(req)) == [4, 7]  # the single token is not a prompt tile
+    start_of = {4: (0, 500), 7: (71, 0)}
+    keys = [start_of[r][1] + (t - start_of[r][0]) + n for r, t, n in zip(req, tok0, ntok)]
+    assert keys == sorted(keys)
+    # every token of the two portions is in exactly one tile
+    covered = sorted(t for t0, n in zip(tok0, ntok) for t in range(t0, t0 + n))
+    assert covered == list(range(0, 70)) + list(range(71, 201))
+    assert ctx.attention_tiles(32, min_tokens=2) is tiles  # cached per (tokens a tile, least tokens)
