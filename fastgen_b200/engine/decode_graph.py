@@ -2,7 +2,8 @@
 
 The reference captures ``decode`` once per batch-size bucket at start-up and
 replays it with inputs copied into fixed tensors (fastgen/generate.py:300-347,
-685-718; fastgen/forward.py:95-151).  The same here, captured lazily: a bucket
+685-718; fastgen/forward.py:95-151).  The same here (``capture_all``; a bucket that was
+not captured then is captured when a step first needs it): a bucket
 of size ``n`` owns fixed device buffers for the tokens, positions and slots of
 ``n`` lanes; a step with fewer requests pads the rest with slot ``-1``, which
 every kernel treats as "no request" (nothing is written to any page).
