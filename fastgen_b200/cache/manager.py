@@ -88,7 +88,7 @@ class CacheGroup:
     table_width: int
     host_table: np.ndarray  # [n_slots, table_width] int32, -1 = no page
     k_pages: Optional[torch.Tensor] = None  # [len(entries), n_pages, Hkv, page, hd]
-    v_pages: Optional[torch.Tensor] = None
+    v_pages: Optional[torch.Tensor] = None  # the second pool; None when the spec asks for one
     device_table: Optional[torch.Tensor] = None  # [n_slots, table_width] int32
     tensor_maps: Optional[tuple] = None  # made by the kernels' side for pools it can tile
     dirty: List[Tuple[int, int, int]] = field(default_factory=list)  # (slot, col, page)
@@ -100,7 +100,7 @@ class CacheGroup:
         return max(0, length - self.spec.window + 1) // self.page_size
 
     def bytes_per_token(self, elt_size: int) -> int:
-        return 2 * len(self.entries) * self.spec.n_kv_heads * self.spec.head_dim * elt_size
+        return self.spec.n_pools * len(self.entries) * self.spec.n_kv_heads * self.spec.head_dim * elt_size
 
 
 @dataclass
@@ -109,7 +109,7 @@ class LayerMemory:
     state tensor of its mixer, both indexed by the request's slot."""
 
     k_pages: Optional[torch.Tensor] = None  # [n_pages, Hkv, page, hd]
-    v_pages: Optional[torch.Tensor] = None
+    v_pages: Optional[torch.Tensor] = None  # None for a one-pool group
     block_table: Optional[torch.Tensor] = None  # [n_slots, width] int32
     page_size: int = 0
     writes: bool = True  # False: the run reads the cache another run writes
@@ -140,8 +140,11 @@ class CacheManager:
 
     ``cache_specs[e]`` / ``state_specs[e]`` give, for schedule entry ``e``, what
     its mixer needs (``None`` if nothing, or if the entry reads another entry's
-    cache -- then ``kv_from[e]`` names it).  ``n_pages`` is the pool size of each
-    group (an int for all groups or one per group).
+    cache -- then ``kv_from[e]`` names it).  ``page_size`` is the page of every group
+    whose spec does not ask for its own.  ``n_pages`` is the pool size of each group: a
+    list with one number per group, or one number, which then counts pages of
+    ``page_size`` tokens and is converted for a group with other pages so that every
+    group holds the same number of tokens.
     """
 
     def __init__(
@@ -177,13 +180,17 @@ class CacheManager:
                 continue
             if spec not in by_spec:
                 by_spec[spec] = len(self.groups)
-                pages = n_pages if isinstance(n_pages, int) else n_pages[len(self.groups)]
-                width = -(-max_length // page_size)
+                group_page = spec.page_size or page_size
+                if isinstance(n_pages, int):
+                    pages = max(1, n_pages * page_size // group_page)
+                else:
+                    pages = n_pages[len(self.groups)]
+                width = -(-max_length // group_page)
                 self.groups.append(
                     CacheGroup(
                         spec=spec,
                         entries=[],
-                        page_size=page_size,
+                        page_size=group_page,
                         pool=PagePool(pages),
                         table_width=width,
                         host_table=np.full((max_requests, width), -1, dtype=np.int32),
@@ -214,16 +221,17 @@ class CacheManager:
                     len(grp.entries),
                     grp.pool.n_pages,
                     grp.spec.n_kv_heads,
-                    page_size,
+                    grp.page_size,
                     grp.spec.head_dim,
                 )
                 grp.k_pages = torch.zeros(shape, dtype=dtype, device=device)
-                grp.v_pages = torch.zeros(shape, dtype=dtype, device=device)
+                if grp.spec.n_pools == 2:
+                    grp.v_pages = torch.zeros(shape, dtype=dtype, device=device)
                 grp.device_table = torch.full(
                     (max_requests, grp.table_width), -1, dtype=torch.int32, device=device
                 )
-                if tensor_map_factory is not None:
-                    grp.tensor_maps = tensor_map_factory(grp.k_pages, grp.v_pages, page_size)
+                if tensor_map_factory is not None and grp.v_pages is not None:
+                    grp.tensor_maps = tensor_map_factory(grp.k_pages, grp.v_pages, grp.page_size)
             for e, st in enumerate(self.state_specs):
                 if st is not None:
                     self.states[e] = torch.zeros(
@@ -375,7 +383,7 @@ class CacheManager:
             mem.writes = self.kv_from[entry] is None
             if grp.k_pages is not None:
                 mem.k_pages = grp.k_pages[i]
-                mem.v_pages = grp.v_pages[i]
+                mem.v_pages = grp.v_pages[i] if grp.v_pages is not None else None
                 mem.block_table = grp.device_table
                 mem.tensor_maps = grp.tensor_maps
                 mem.layer_index = i

@@ -104,6 +104,7 @@ def llama_model_args(config: Mapping[str, Any]) -> ModelArgs:
             head_dim=head_dim,
             position=rope,
             window=window,
+            qk_layout="half_split",  # how Hugging Face Llama checkpoints store q_proj and k_proj
         )
     except ValueError as e:
         raise ConfigError(str(e)) from None

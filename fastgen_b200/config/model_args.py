@@ -13,7 +13,7 @@ parameters so that layers may differ.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Optional, Sequence
+from typing import Any, Mapping, Optional, Sequence, Tuple
 
 
 class ConfigError(ValueError):
@@ -37,13 +37,23 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement (``block``) and its four parts."""
+    """One layer: the arrangement (``block``) and its parts.
+
+    Every layer has one mixer (it is what owns the layer's cache or state), one
+    feed-forward and their two norms.  An arrangement that needs more parts (norms
+    after the mixer and the feed-forward, a second feed-forward, ...) names them in
+    ``extra`` as ``(name, role, spec)`` with ``role`` one of ``"norm"``,
+    ``"feed_forward"``, ``"mixer"``; the block receives them as keyword arguments
+    under ``name`` and their tensors are loaded like everybody's.  (A mixer given
+    there gets no cache or state of its own.)
+    """
 
     block: str
     mixer: PartSpec
     mixer_norm: PartSpec
     ffn: PartSpec
     ffn_norm: PartSpec
+    extra: Tuple[Tuple[str, str, PartSpec], ...] = ()
 
 
 @dataclass(frozen=True)

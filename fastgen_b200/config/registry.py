@@ -59,5 +59,16 @@ def read_config(model_dir: Union[str, Path]) -> Dict[str, Any]:
 
 
 def load_model_args(model_dir: Union[str, Path]) -> ModelArgs:
-    """Read ``model_dir/config.json`` and build the model description."""
-    return model_args_from_config(read_config(model_dir))
+    """Read ``model_dir/config.json`` and build the model description.  A ``vocab_size``
+    of -1 stands for the size of the folder's tokenizer (fastgen/generate.py:153-154)."""
+    config = read_config(model_dir)
+    if config.get("vocab_size") == -1:
+        path = Path(model_dir) / "tokenizer.json"
+        if not path.is_file():
+            raise ConfigError(
+                f"config.json gives vocab_size -1 (the tokenizer's), but {path} does not exist"
+            )
+        from tokenizers import Tokenizer
+
+        config = dict(config, vocab_size=Tokenizer.from_file(str(path)).get_vocab_size())
+    return model_args_from_config(config)

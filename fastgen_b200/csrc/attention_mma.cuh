@@ -375,22 +375,37 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, int by
       "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// Bounded wait: gives up after ~2^22 polls, records it and lets the block finish
-// (its copies have either landed or the data is reported as unusable).
+// Bounded wait.  It gives up after `limit` polls, ORs FG_STATUS_WAIT_TIMEOUT into the status
+// word and sets `*gave_up`, a flag in the block's shared memory (zero at the block's start).
+// Once the flag is set every other wait of the block that is given the flag returns false
+// at its next poll instead of counting to the limit itself: a block whose copies or
+// products never arrive loses the time of one wait, runs through the rest of its loops on
+// whatever its buffers hold (the status word tells the host that the step's results are void),
+// and returns.  No control flow depends on the flag, so named barriers stay matched.
 //
 // A parity wait can only tell "this phase is over" from "not yet" while the waiter is less
 // than two completions behind the barrier: a barrier must not complete a second time before
 // a waiter of the first completion has looked (give every stage a barrier of its own).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, int* status) {
-  for (int it = 0; it < (1 << 22); ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
+constexpr int MBAR_WAIT_POLLS = 1 << 22;
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, int parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, int* status, int* gave_up = nullptr,
+                                          int limit = MBAR_WAIT_POLLS) {
+  if (mbar_try_wait(bar, parity)) return true;  // the usual case costs what it did without the flag
+  for (int it = 1; it < limit; ++it) {
+    if (gave_up != nullptr && *reinterpret_cast<volatile int*>(gave_up) != 0) return false;
+    if (mbar_try_wait(bar, parity)) return true;
   }
+  if (gave_up != nullptr) *reinterpret_cast<volatile int*>(gave_up) = 1;
   if (status) atomicOr(status, FG_STATUS_WAIT_TIMEOUT);
   return false;
 }

@@ -91,10 +91,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // p_ready: all 128 softmax threads stored its probabilities; o_done: its P V is done.
   // Every barrier completes once a key tile, and the block counts its key tiles through
   // all the work it takes (`base` below): stage and parity follow that running number.
-  __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done[2];
+  // drained: used once, at the end of a block one of whose waits ran out.
+  __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done[2], drained;
   __shared__ uint32_t tmem_base_s;
   __shared__ int first_pos_s;
   __shared__ unsigned int work_s;
+  __shared__ int gave_up;  // set by a wait that ran out: the waits after it return at once (see mbar_wait)
   constexpr int PAGE_STAGE = 256;
   __shared__ int box_pages[PAGE_STAGE];
 
@@ -108,6 +110,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     tmem_relinquish();
   }
   if (tid == SOFTMAX_THREADS) {
+    gave_up = 0;
     mbar_init(&full_k[0], 1);
     mbar_init(&full_k[1], 1);
     mbar_init(&full_v[0], 1);
@@ -121,6 +124,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     // completions behind (the next one, O_{t+2}'s, needs that waiter's own work)
     mbar_init(&o_done[0], 1);
     mbar_init(&o_done[1], 1);
+    mbar_init(&drained, 1);
     mbar_fence_init();
   }
   tc_fence_before();
@@ -138,6 +142,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const unsigned int total_work = (unsigned int)n_tiles_total * n_kv_heads * n_subs;
   const unsigned int last_draw = (total_work > gridDim.x ? total_work - gridDim.x : 0u) + gridDim.x - 1;
   int base = 0;  // key tiles this block has been through before the current item
+  bool dead = false;  // a wait of this block ran out during an earlier item
 
   for (unsigned int work = blockIdx.x; work < total_work;) {
     const int g = work % n_kv_heads;
@@ -147,7 +152,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     int n_tiles = 0;
 
-    if (b >= 0) {  // (uniform over the block)
+    // (uniform over the block; after a wait ran out the block only draws its items, so that
+    // the counter still returns to zero)
+    if (b >= 0 && !dead) {
       auto row_token = [&](int r) { return r / heads_per_block; };
       auto row_head = [&](int r) { return sub * heads_per_block + (r % heads_per_block); };
       auto row_valid = [&](int r) { return row_token(r) < ntok && row_head(r) < group; };
@@ -253,21 +260,21 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
                 const int slot = (k_lo + t * KEYS) & (page_size - 1);
                 unsigned char* kb = Ks + stage * STAGE_BYTES;
                 unsigned char* vb = Vs + stage * STAGE_BYTES;
-                if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status);
+                if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status, &gave_up);
                 mbar_arrive_expect(&full_k[stage], k_bytes);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
                   tma_load_5d(kb + h * KV_HALF, &k_map, h * 64, slot, g, page, layer, &full_k[stage]);
-                if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status);
+                if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status, &gave_up);
                 mbar_arrive_expect(&full_v[stage], k_bytes);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
                   tma_load_5d(vb + h * KV_HALF, &v_map, h * 64, slot, g, page, layer, &full_v[stage]);
               }
             } else {
-              if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status);
+              if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status, &gave_up);
               load_tile(t, box_pages + staged, false);
-              if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status);
+              if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status, &gave_up);
               load_tile(t, box_pages + staged, true);
             }
             if (++staged == tiles_per_fill) staged = 0;
@@ -278,9 +285,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
             if (staged == 0) fill_pages(t);
             const int* pages = box_pages + staged * n_boxes;
             const int gt = base + t, stage = gt & 1;
-            if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status);
+            if (gt >= 2) mbar_wait(&s_done[stage], ((gt - 2) >> 1) & 1, status, &gave_up);
             load_tile(t, pages, false);
-            if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status);
+            if (gt >= 2) mbar_wait(&o_done[stage], ((gt - 2) >> 1) & 1, status, &gave_up);
             load_tile(t, pages, true);
             if (++staged == tiles_per_fill) staged = 0;
           }
@@ -294,7 +301,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           const uint64_t q_desc = smem_desc(Qs, 16), k_desc = smem_desc(Ks, 16), v_desc = smem_desc(Vs, KV_HALF);
           auto issue_s = [&](int t) {
             const int gt = base + t, stage = gt & 1;
-            mbar_wait(&full_k[stage], (gt >> 1) & 1, status);
+            mbar_wait(&full_k[stage], (gt >> 1) & 1, status, &gave_up);
             tc_fence_after();
             const uint64_t kd = k_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
@@ -308,8 +315,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
             const int gt = base + t, stage = gt & 1;
             if (t + 1 < n_tiles) issue_s(t + 1);
             // all softmax threads have stored P_t (and rescaled O where needed)
-            mbar_wait(&p_ready[stage], (gt >> 1) & 1, status);
-            mbar_wait(&full_v[stage], (gt >> 1) & 1, status);
+            mbar_wait(&p_ready[stage], (gt >> 1) & 1, status, &gave_up);
+            mbar_wait(&full_v[stage], (gt >> 1) & 1, status, &gave_up);
             tc_fence_after();
             const uint64_t vd = v_desc + (uint64_t)((stage * STAGE_BYTES) >> 4);
 #pragma unroll
@@ -335,7 +342,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         for (int t = 0; t < n_tiles; ++t) {
           const int gt = base + t, stage = gt & 1;
           const uint32_t s_addr = tmem + my_lane + COL_S0 + stage * KEYS;
-          mbar_wait(&s_done[stage], (gt >> 1) & 1, status);
+          mbar_wait(&s_done[stage], (gt >> 1) & 1, status, &gave_up);
           tc_fence_after();
           const int k0 = k_lo + t * KEYS;
           float s[KEYS];
@@ -396,7 +403,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           // O_{t-1} is complete after this wait; O is then rescaled where a row's reference
           // maximum was raised (warp-uniform decision).  (The barrier of this parity completes
           // next for O_{t+1}, which needs this thread's P_{t+1}: the wait cannot fall behind.)
-          if (t > 0) mbar_wait(&o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1, status);
+          if (t > 0) mbar_wait(&o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1, status, &gave_up);
           if (t > 0 && __any_sync(0xffffffffu, raise)) {
             tc_fence_after();
 #pragma unroll
@@ -413,7 +420,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         }
         // ---- O / l -> out ----
         const int gl = base + n_tiles - 1;
-        mbar_wait(&o_done[gl & 1], (gl >> 1) & 1, status);
+        mbar_wait(&o_done[gl & 1], (gl >> 1) & 1, status, &gave_up);
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         __nv_bfloat16* dst =
@@ -448,6 +455,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     }
     __syncthreads();
     work = work_s;
+    dead = *reinterpret_cast<volatile int*>(&gave_up) != 0;
+  }
+  if (dead && tid == MMA_WARP * 32) {
+    // products issued after the wait that ran out may still be running: the tensor memory is
+    // given back only once they are through (or this wait runs out too)
+    umma_commit(&drained);
+    for (int it = 0; it < MBAR_WAIT_POLLS && !mbar_try_wait(&drained, 0); ++it) {
+    }
   }
   tc_fence_before();
   __syncthreads();

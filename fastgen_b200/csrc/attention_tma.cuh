@@ -113,6 +113,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(Vs + HALVES * HALF_BYTES);
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ int box_page[SPLIT / 8];  // page of each box, -1: nothing to load
+  __shared__ int gave_up;              // set by a wait that ran out (see mbar_wait)
 
   // positions, slots and block tables are inputs of the step (no kernel of the step
   // writes them), so the page look-ups and the barrier set-up run while the kernel
@@ -146,6 +147,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     box_page[tid] = page;
   }
   if (tid == 0) {
+    gave_up = 0;
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_fence_init();
@@ -200,7 +202,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   for (int kk = 0; kk < HD / 16; ++kk)
     ldmatrix_x4(qf[kk], Qs + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
 
-  mbar_wait(&bars[0], 0, status);
+  mbar_wait(&bars[0], 0, status, &gave_up);
   float s[NT][4];
   qk_product_swz<HD, NT>(s, qf, Ks, warp * 32, lane);
 #pragma unroll
@@ -216,7 +218,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   softmax_step<HD, NT>(s, o, m, l);
-  mbar_wait(&bars[1], 0, status);
+  mbar_wait(&bars[1], 0, status, &gave_up);
   pv_product_swz<HD, NT>(o, s, Vs, warp * 32, lane);
 
   // merge the 4 warps through shared memory (the keys' space is free now)
@@ -324,10 +326,12 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
   // per request: the token's position (-1: padding lane) and the number of (request, split)
   // pairs before it
   __shared__ int s_pos[PS_MAX_SEQS], s_cum[PS_MAX_SEQS + 1];
+  __shared__ int gave_up;  // set by a wait that ran out: the waits after it return at once (see mbar_wait)
 
   pdl_trigger();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
+    gave_up = 0;
     for (int i = 0; i < PS_SLOTS; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 4);  // one arrival a consumer warp
@@ -431,7 +435,7 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {
         const int slot = n_fill % PS_SLOTS;
-        if (n_fill >= PS_SLOTS) mbar_wait(&empty[slot], (n_fill / PS_SLOTS - 1) & 1, status);
+        if (n_fill >= PS_SLOTS) mbar_wait(&empty[slot], (n_fill / PS_SLOTS - 1) & 1, status, &gave_up);
         unsigned char* dst = ring + slot * SLOT_BYTES;
         // boxes with nothing to load hold zeros (a masked probability times garbage could be NaN)
         if (valid != (n_boxes >= 32 ? 0xffffffffu : (1u << n_boxes) - 1u)) {
@@ -484,7 +488,7 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
       const unsigned char* Vs = ring + slot_v * SLOT_BYTES;
 
       // S^T[keys, heads] = K Q^T for this warp's 32 keys
-      mbar_wait(&full[slot_k], (fk / PS_SLOTS) & 1, status);
+      mbar_wait(&full[slot_k], (fk / PS_SLOTS) & 1, status, &gave_up);
       float s[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
@@ -544,7 +548,7 @@ attention_decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map,
       }
 
       // O^T[dims, heads] = V^T P^T
-      mbar_wait(&full[slot_v], (fv / PS_SLOTS) & 1, status);
+      mbar_wait(&full[slot_v], (fv / PS_SLOTS) & 1, status, &gave_up);
       float o[HD / 16][4];
 #pragma unroll
       for (int dt = 0; dt < HD / 16; ++dt) {
@@ -680,6 +684,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
   __shared__ int row_pos[PF_ROWS];
   constexpr int PAGE_STAGE = 512;             // box page ids kept in shared memory at a time
   __shared__ int box_pages[PAGE_STAGE];
+  __shared__ int gave_up;  // set by a wait that ran out (see mbar_wait)
 
   // the tile list is in ascending order of work and blockIdx.x runs fastest: all key/value
   // heads of the heaviest tile start first
@@ -705,6 +710,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
     *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
   }
   if (tid == 0) {
+    gave_up = 0;
     mbar_init(&full[0], 1);
     mbar_init(&full[1], 1);
     mbar_fence_init();
@@ -814,7 +820,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __
       __syncthreads();
     }
     if (t + 1 < n_tiles && tid == 0) issue(t + 1);  // its stage was released by the barrier below
-    mbar_wait(&full[t & 1], (t >> 1) & 1, status);
+    mbar_wait(&full[t & 1], (t >> 1) & 1, status, &gave_up);
     const int k0 = k_lo + t * PF_KEYS;
     if (k0 <= warp_max) {
       const unsigned char* ks = Ks + (t & 1) * STAGE_BYTES;

@@ -41,9 +41,9 @@ CORE_SOURCES = [
     "silu_gate.cu",
     "gemm_f32.cu",
     "gemm_skinny.cu",
-    "gemm_stream.cu",
     "sampling.cu",
     "tensor_map.cu",
+    "selftest.cu",
 ]
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -50,8 +50,8 @@ _CORE_SIGNATURES = {
     "fg_gemm_skinny_swiglu_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "fg_gemm_skinny_qkv_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                                 _P, _P],
-    "fg_gemm_stream_bf16": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _I, _P, _P],
-    "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P],
+    "fg_sample": [_P, _I, _I, _I, _P, _F, c_ulonglong, _P, _P, _P, _P, _P, _P, _P],
+    "fg_selftest_wait_timeout": [_I, _P, _P, _P],
     "fg_sample_uniform": [c_ulonglong, _P, _P, _P, _I, _P],
     "fg_make_kv_tensor_map": [_P, _P, _I, _I, _I, _I, _I, _I],
 }
@@ -90,6 +90,22 @@ def _declare(lib: ctypes.CDLL, signatures) -> None:
 
 class KernelError(RuntimeError):
     pass
+
+
+def describe_status(word: int) -> str:
+    """The faults that the bits of a status word stand for, in words."""
+    faults = []
+    if word & STATUS_BAD_PAGE:
+        faults.append("a block-table entry was missing or out of range")
+    if word & STATUS_BAD_TOKEN:
+        faults.append("a token id was outside the vocabulary")
+    if word & STATUS_WAIT_TIMEOUT:
+        faults.append("a bounded wait inside a kernel gave up")
+    if word & STATUS_BAD_SPLITS:
+        faults.append("decode attention was launched with too few splits")
+    if word & ~(STATUS_BAD_PAGE | STATUS_BAD_TOKEN | STATUS_WAIT_TIMEOUT | STATUS_BAD_SPLITS):
+        faults.append(f"unknown bits {word:#x}")
+    return "kernel status: " + "; ".join(faults)
 
 
 class TensorMap:
@@ -183,14 +199,9 @@ class Ops:
         self.lib = core()
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._scratch = {}
-        self._stream_scratch = None
-        self._stream_counters = None
         # the prompt attention kernel's blocks draw their work from it; zero between launches
         self._work_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
-        # FG_STREAM_GEMM: "all" uses the tcgen05 weight-streaming product for every product of
-        # 9..256 tokens, "auto" where it measured faster than the library, default: never
-        self.stream_gemm = os.environ.get("FG_STREAM_GEMM", "off")
         # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -201,16 +212,16 @@ class Ops:
         word = int(self.status.item())
         if word:
             self.status.zero_()
-            faults = []
-            if word & STATUS_BAD_PAGE:
-                faults.append("a block-table entry was missing or out of range")
-            if word & STATUS_BAD_TOKEN:
-                faults.append("a token id was outside the vocabulary")
-            if word & STATUS_WAIT_TIMEOUT:
-                faults.append("a bounded wait inside a kernel gave up")
-            if word & STATUS_BAD_SPLITS:
-                faults.append("decode attention was launched with too few splits")
-            raise KernelError("kernel status: " + "; ".join(faults))
+            raise KernelError(describe_status(word))
+
+    def wait_timeout_selftest(self, limit: int = 1024):
+        """Run a bounded wait on a barrier nobody arrives at (``limit`` polls) and return
+        what the kernel saw: (first wait returned, second wait returned, cycles of the
+        first, cycles of the second, wait on a completed phase returned).  The status word
+        then holds the time-out bit."""
+        out = torch.zeros(5, dtype=torch.int64, device=self.device)
+        _check(self.lib, self.lib.fg_selftest_wait_timeout(int(limit), _ptr(self.status), _ptr(out), _stream()))
+        return out.tolist()
 
     # -- kernels ---------------------------------------------------------------
     def embedding(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -268,10 +279,6 @@ class Ops:
                 _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out.dtype),
                 m, n, k, _stream()))
             return out
-        if self._stream_ok(m, n, k, x, w):
-            # a decode batch against a very tall matrix (the vocabulary): this package's tcgen05
-            # weight-streaming product; elsewhere the library's is as fast or faster
-            return self.linear_stream(x, w, out=out, out_dtype=want)
         if want == torch.bfloat16:
             return torch.mm(x, w.t(), out=out) if out is not None else torch.mm(x, w.t())
         # float32 result of a bfloat16 product (logits)
@@ -280,42 +287,6 @@ class Ops:
             out.copy_(res)
             return out
         return res
-
-    def _stream_ok(self, m: int, n: int, k: int, x: torch.Tensor, w: torch.Tensor) -> bool:
-        if self.stream_gemm == "off":
-            return False
-        fits = (k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1
-                and w.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-        if self.stream_gemm == "all":
-            return fits and SKINNY_MAX_M < m <= 256
-        if self.stream_gemm == "auto":
-            # where it measured faster than the library: the vocabulary projection of 48..96 tokens
-            return fits and 48 <= m <= 96 and n * k >= (1 << 28)
-        return False
-
-    def linear_stream(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-                      out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """``x @ w.T`` for up to 256 tokens with this package's tcgen05 weight-streaming
-        product (bfloat16 operands; the work is cut evenly over the SMs)."""
-        m, k = x.shape
-        n = w.shape[0]
-        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
-        assert x.stride(1) == 1 and w.stride(1) == 1
-        if out is None:
-            out = torch.empty((m, n), dtype=out_dtype or torch.bfloat16, device=x.device)
-        assert out.stride(1) == 1
-        if self._stream_scratch is None:
-            lib = self.lib
-            lib.fg_gemm_stream_scratch_floats.restype = ctypes.c_longlong
-            floats = lib.fg_gemm_stream_scratch_floats(lib.fg_gemm_stream_max_m())
-            self._stream_scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
-            # arrival counts: zero before the first call, left at zero by every call
-            self._stream_counters = torch.zeros(8192, dtype=torch.int32, device=self.device)
-        _check(self.lib, self.lib.fg_gemm_stream_bf16(
-            _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _code(out.dtype), m, n, k,
-            _ptr(self._stream_scratch), self._stream_scratch.numel(), _ptr(self._stream_counters),
-            self._stream_counters.numel(), _ptr(self.status), _stream()))
-        return out
 
     def _skinny_ok(self, x: torch.Tensor, w: torch.Tensor, k: int) -> bool:
         return (x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_M and k % 8 == 0
@@ -464,7 +435,7 @@ class Ops:
             # exist: the scratch follows the keys in the cache, not requests x longest request
             pairs = 0
             if tma and lib.fg_attention_decode_is_persistent(singles.n, n_heads, n_kv_heads, page_size):
-                pairs = min(singles.n * max_splits, singles.max_pairs or singles.n * max_splits)
+                pairs = min(singles.n * max_splits, singles.stretches(DECODE_SPLIT))
             floats = lib.fg_attention_decode_scratch_floats(singles.n, max_splits, n_heads, pairs)
             scratch = self._decode_scratch(floats)
             head = (_ptr(singles.req), _ptr(singles.tok), singles.n, n_heads, n_kv_heads, head_dim,
@@ -481,10 +452,13 @@ class Ops:
             Ops.launches += 1  # the combine kernel
 
     def sample(self, logits, temps, top_p: float, seed: int, req_keys, positions,
-               out_tokens, out_logprobs=None, scratch=None) -> torch.Tensor:
+               out_tokens, out_logprobs=None, scratch=None, with_status: bool = False) -> torch.Tensor:
+        """One token per row of ``logits`` into ``out_tokens``.  ``with_status``: the
+        device status word is copied to ``out_tokens[rows]`` (one more entry), so that the
+        host's read of the tokens also tells it whether a kernel of the step recorded a fault."""
         rows, vocab = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1
-        assert out_tokens.dtype == torch.int32
+        assert out_tokens.dtype == torch.int32 and out_tokens.numel() >= rows + int(with_status)
         if temps is not None:
             assert temps.dtype == torch.float32 and scratch is not None
             assert scratch.numel() >= rows * vocab and scratch.dtype == torch.float32
@@ -493,7 +467,7 @@ class Ops:
         _check(self.lib, self.lib.fg_sample(
             _ptr(logits), logits.stride(0), rows, vocab, _ptr(temps), float(top_p),
             int(seed) & 0xFFFFFFFFFFFFFFFF, _ptr(req_keys), _ptr(positions), _ptr(out_tokens),
-            _ptr(out_logprobs), _ptr(scratch), _stream()))
+            _ptr(out_logprobs), _ptr(scratch), _ptr(self.status) if with_status else None, _stream()))
         return out_tokens
 
     def sample_uniform(self, seed: int, req_keys, positions) -> torch.Tensor:

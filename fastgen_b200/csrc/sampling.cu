@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temps,
               float top_p, unsigned long long seed, const long long* __restrict__ req_keys,
               const int* __restrict__ positions, int* __restrict__ out_tokens,
-              float* __restrict__ out_logprobs, float* __restrict__ probs_scratch) {
+              float* __restrict__ out_logprobs, float* __restrict__ probs_scratch, const int* status_word) {
   __shared__ float fs[32];
   __shared__ ArgMax as[32];
   __shared__ float chunk_sums[THREADS];
@@ -171,6 +171,9 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     if (tid == 0) out_logprobs[row] = x[token] - xmax - logf(z1);
   }
   if (tid == 0) out_tokens[row] = token;
+  // The status word of the step's kernels rides along with the tokens: the host reads both
+  // with one copy.  (Every kernel of the step is ahead of this one on the stream.)
+  if (status_word != nullptr && row == 0 && tid == 0) out_tokens[gridDim.x] = *status_word;
 }
 
 __global__ void uniform_kernel(unsigned long long seed, const long long* req_keys, const int* positions,
@@ -184,17 +187,18 @@ __global__ void uniform_kernel(unsigned long long seed, const long long* req_key
 // logits: [rows, ld] float32 (ld >= vocab).  temps: [rows] or null (null or
 // temp <= 0: greedy).  req_keys/positions: what the draw is keyed by.
 // probs_scratch: [rows, vocab] float32, needed when any row samples.
-// out_logprobs: [rows] or null.
+// out_logprobs: [rows] or null.  status_word: null, or a device int whose value is copied
+// to out_tokens[rows] (out_tokens then has rows + 1 entries).
 extern "C" int fg_sample(const float* logits, int ld, int rows, int vocab, const float* temps,
                          float top_p, unsigned long long seed, const long long* req_keys,
                          const int* positions, int* out_tokens, float* out_logprobs,
-                         float* probs_scratch, cudaStream_t stream) {
+                         float* probs_scratch, const int* status_word, cudaStream_t stream) {
   if (rows == 0) return 0;
   FG_CHECK_ARG(vocab > 0 && ld >= vocab, "fg_sample: bad sizes vocab=%d ld=%d", vocab, ld);
   FG_CHECK_ARG(temps == nullptr || probs_scratch != nullptr, "fg_sample: sampling needs scratch");
   FG_CHECK_ARG(top_p > 0.f, "fg_sample: top_p must be positive, got %f", (double)top_p);
   sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, temps, top_p, seed, req_keys,
-                                              positions, out_tokens, out_logprobs, probs_scratch);
+                                              positions, out_tokens, out_logprobs, probs_scratch, status_word);
   FG_CHECK_LAUNCH("fg_sample");
   return 0;
 }
@@ -250,7 +254,7 @@ extern "C" int fg_sample_noalloc(const float* logits, int ld, int rows, int voca
     g_noalloc_ptr[device] = ptr;
   }
   sample_kernel<<<rows, THREADS, 0, stream>>>(logits, ld, vocab, temps, top_p, seed, req_keys, positions,
-                                              out_tokens, out_logprobs, g_noalloc_ptr[device]);
+                                              out_tokens, out_logprobs, g_noalloc_ptr[device], nullptr);
   FG_CHECK_LAUNCH("fg_sample_noalloc");
   return 0;
 }

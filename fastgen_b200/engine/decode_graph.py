@@ -19,7 +19,6 @@ import numpy as np
 import torch
 
 from ..csrc.ops import Ops
-from ..csrc.ops import DECODE_SPLIT
 from .step import AttentionTiles, SingleTokens, StepContext
 
 
@@ -36,10 +35,10 @@ _RING = 8
 
 
 class _Bucket:
-    def __init__(self, size: int, max_len: int, max_pairs: int, device) -> None:
+    def __init__(self, size: int, max_len: int, keys_bound: int, device) -> None:
         self.size = size
         self.max_len = max_len  # positions the captured launch grids cover
-        self.max_pairs = max_pairs  # (request, stretch of 128 positions) pairs the scratch holds
+        self.keys_bound = keys_bound  # cached positions the lanes can hold together
         # one packed buffer: tokens | pos | req | arange | ones
         # a ring of pinned staging buffers: a buffer is rewritten only after the
         # copy that last read it has run, so the host may run ahead of the device
@@ -66,7 +65,7 @@ class _Bucket:
         tiles = AttentionTiles(ctx.req, self.dev[3 * n : 4 * n], self.dev[4 * n :], n)
         none = AttentionTiles(None, None, None, 0)
         ctx.attention_tiles = lambda tokens_per_tile, min_tokens=1: tiles if min_tokens <= 1 else none
-        singles = SingleTokens(ctx.req, self.dev[3 * n : 4 * n], n, self.max_len, self.max_pairs)
+        singles = SingleTokens(ctx.req, self.dev[3 * n : 4 * n], n, self.max_len, None, self.keys_bound)
         ctx.single_tokens = lambda: singles
         return ctx
 
@@ -90,6 +89,7 @@ class DecodeGraphs:
         self.capture_stream = None
         self.warmed = set()  # batch sizes that ran once outside a capture
         self.replays = 0
+        self.padded_replays = 0  # replays of a bucket larger than the step (lanes of slot -1)
         self.last_h2d_bytes = 0
 
     def run(self, tokens, positions: Sequence[int], slots: Sequence[int]) -> torch.Tensor:
@@ -99,6 +99,11 @@ class DecodeGraphs:
         n = len(positions)
         size = self.sizes[bisect.bisect_left(self.sizes, n)]
         b = self._bucket(size)
+        if b.graph is None:
+            # before the step's inputs are copied in: the warm-up run and the capture see
+            # padding lanes only (slot -1), so no request's keys, values or state are
+            # touched by a forward pass that is not the step's own
+            self._capture(b)
         slot = b.ring_next
         b.ring_next = (slot + 1) % _RING
         if b.ring_events[slot] is not None:
@@ -120,18 +125,16 @@ class DecodeGraphs:
         ev = torch.cuda.Event()
         ev.record()
         b.ring_events[slot] = ev
-        if b.graph is None:
-            self._capture(b)
         b.graph.replay()
         Ops.launches += b.n_kernels
         self.replays += 1
+        self.padded_replays += size > n
         return b.logits[:n]
 
     def _bucket(self, size: int) -> _Bucket:
         b = self.buckets.get(size)
         if b is None:
-            pairs = min(size * -(-self.max_len // DECODE_SPLIT), self.cache_tokens // DECODE_SPLIT + size)
-            b = self.buckets[size] = _Bucket(size, self.max_len, pairs, self.device)
+            b = self.buckets[size] = _Bucket(size, self.max_len, self.cache_tokens, self.device)
         return b
 
     def capture_all(self) -> None:
@@ -144,6 +147,7 @@ class DecodeGraphs:
 
     def _capture(self, b: _Bucket) -> None:
         model, memories, size = self.model, self.memories, b.size
+        b.dev[2 * size : 3 * size] = -1  # every lane is padding while warming up and capturing
         ctx = b.context(self.device)
         if size not in self.warmed:
             # once eagerly for a batch size (libraries load and choose their kernels,

@@ -29,6 +29,7 @@ from typing import Any, Generator, List, Optional, Union
 import torch
 
 from ..config import load_model_args, read_config
+from ..csrc.ops import describe_status
 from ..sampling import Sampler
 from ..utils.misc import hashints
 from .model import Model
@@ -309,6 +310,10 @@ class Fastgen:
             tokens = out  # stays on the device
         sampled = torch.stack(outs).tolist()  # the run's one device-to-host read
         logprobs = torch.stack(lps).tolist() if lps[0] is not None else None
+        # the last entry of a step's row is the device status word after that step
+        word = 0
+        for row in sampled:
+            word |= row.pop()
         self.steps += n_steps
         t_end = time.perf_counter()
         for k in range(n_steps):
@@ -316,9 +321,23 @@ class Fastgen:
                 t_start=t_start + (t_end - t_start) * k / n_steps,
                 t_end=t_start + (t_end - t_start) * (k + 1) / n_steps,
                 decode_tokens=len(reqs), prompt_tokens=0,
-                h2d_bytes=engine.graphs.last_h2d_bytes, d2h_bytes=4 * len(reqs),
+                h2d_bytes=engine.graphs.last_h2d_bytes, d2h_bytes=4 * (len(reqs) + 1),
             ))
+        if word:
+            yield from self._fail_step(reqs, word)
+            return
         for req in sched.commit_decode_run(reqs, sampled, logprobs):
+            yield self._packet(req)
+
+    def _fail_step(self, reqs, word: int):
+        """A kernel of the step recorded a fault in the status word (a missing page, a token
+        outside the vocabulary, a wait that ran out) instead of performing a bad access: what
+        the step computed is void.  Its requests end with ``Packet.error``; the word is
+        cleared, the others go on."""
+        message = describe_status(word)
+        logger.error("%s; ending %d request(s) of the step", message, len(reqs))
+        self.ops.status.zero_()
+        for req in self.scheduler.fail(reqs, message):
             yield self._packet(req)
 
     @torch.inference_mode()
@@ -358,6 +377,7 @@ class Fastgen:
             sampling = [e for e in plan if e.samples]
             tokens: List[int] = []
             logprobs = None
+            word = 0
             if sampling:
                 out, lp = self.sampler.sample(
                     logits,
@@ -366,14 +386,18 @@ class Fastgen:
                     [len(e.request) for e in sampling],
                 )
                 tokens = out.tolist()  # the step's one device-to-host read
+                word = tokens.pop()  # the device status word rides along
                 logprobs = lp.tolist() if lp is not None else None
             n_decode = sum(1 for e in plan if len(e.tokens) == 1 and e.samples and e.request.generated)
             self.step_log.append(dict(
                 t_start=t_start, t_end=time.perf_counter(), decode_tokens=n_decode,
                 prompt_tokens=sum(len(e.tokens) for e in plan) - n_decode,
-                h2d_bytes=self.engine.last_h2d_bytes, d2h_bytes=4 * len(tokens),
+                h2d_bytes=self.engine.last_h2d_bytes, d2h_bytes=4 * (len(tokens) + 1) if sampling else 0,
             ))
             if len(self.step_log) > 100_000:
                 del self.step_log[:50_000]
+            if word:
+                yield from self._fail_step([e.request for e in plan], word)
+                continue
             for req in sched.commit(plan, tokens, logprobs):
                 yield self._packet(req)

@@ -27,9 +27,17 @@ from ..parts.base import (
 from ..weights.loader import load_weights
 
 
+_MAKERS = {"mixer": make_mixer, "norm": make_norm, "feed_forward": make_feed_forward}
+
+
 def _build_blocks(args: ModelArgs) -> List[Block]:
     blocks = []
     for layer in args.layers:
+        extra = {}
+        for name, role, spec in layer.extra:
+            if role not in _MAKERS:
+                raise ValueError(f"part {name!r} of a layer has role {role!r}; known: {sorted(_MAKERS)}")
+            extra[name] = _MAKERS[role](spec)
         blocks.append(
             make_block(
                 layer.block,
@@ -37,6 +45,7 @@ def _build_blocks(args: ModelArgs) -> List[Block]:
                 make_norm(layer.mixer_norm),
                 make_feed_forward(layer.ffn),
                 make_norm(layer.ffn_norm),
+                **extra,
             )
         )
     return blocks
@@ -98,7 +107,7 @@ class Model:
         total = 0
         for spec, src in zip(self.cache_specs(), self.kv_from()):
             if spec is not None and src is None:
-                total += 2 * spec.n_kv_heads * spec.head_dim * elt_size
+                total += spec.n_pools * spec.n_kv_heads * spec.head_dim * elt_size
         return total
 
     def weight_bytes(self) -> int:

@@ -286,6 +286,19 @@ class Scheduler:
                 done.append(req)
         return done
 
+    def fail(self, requests: Sequence[Request], message: str) -> List[Request]:
+        """End running requests with an error (a kernel of their step recorded a fault, so
+        what the step computed for them cannot be trusted): pages and slots are given back."""
+        done: List[Request] = []
+        for req in requests:
+            if req not in self.running:
+                continue
+            self.cache.release(id(req))
+            self.running.remove(req)
+            req.error = message
+            done.append(req)
+        return done
+
     def take_finished(self) -> List[Request]:
         out, self.finished = self.finished, []
         return out

@@ -20,7 +20,6 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, OutOfPages, RequestCache
-from ..csrc.ops import attention_tiling
 from .model import Model
 
 
@@ -52,16 +51,35 @@ class AttentionTiles:
 @dataclass
 class SingleTokens:
     """The step's sequences of one token: their slots and token indices on the
-    device, and the longest of them (cached tokens + 1) on the host."""
+    device, and on the host the longest of them (cached tokens + 1) and what is
+    known of all their lengths: the lengths themselves, or (for a captured graph,
+    which serves every length) ``keys_bound``, the most cached positions these
+    sequences can hold together (0: unknown)."""
 
     req: Optional[torch.Tensor]
     tok: Optional[torch.Tensor]
     n: int
     max_len: int
-    #: an upper bound on the (sequence, stretch of 128 cached positions) pairs of these
-    #: sequences together (0: unknown); kernels that keep partial results per pair size
-    #: their scratch by it
-    max_pairs: int = 0
+    lengths: Optional[List[int]] = None
+    keys_bound: int = 0
+    _stretches: Dict[int, int] = field(default_factory=dict)
+
+    def stretches(self, stretch: int) -> int:
+        """An upper bound on the (sequence, stretch of ``stretch`` consecutive positions)
+        pairs that hold keys of these sequences.  Kernels that cut a sequence's keys into
+        fixed stretches and keep a partial result per pair size their scratch by it."""
+        got = self._stretches.get(stretch)
+        if got is None:
+            per_seq = -(-self.max_len // stretch)
+            got = self.n * per_seq
+            if self.lengths is not None:
+                got = sum(-(-n // stretch) for n in self.lengths)
+            elif self.keys_bound:
+                # a sequence that holds k positions (all of them, or a window's) reaches into
+                # at most k / stretch + 2 stretches
+                got = min(got, self.keys_bound // stretch + 2 * self.n)
+            self._stretches[stretch] = got
+        return got
 
 
 class StepContext:
@@ -123,21 +141,19 @@ class StepContext:
     def single_tokens(self) -> "SingleTokens":
         """The sequences that bring exactly one token (decoded tokens)."""
         if self._singles is None:
-            req, tok, max_len, pairs = [], [], 0, 0
+            req, tok, lengths = [], [], []
             for b, slot in enumerate(self.host_seq_slot):
                 start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
                 if end - start == 1:
                     req.append(slot)
                     tok.append(start)
-                    length = self.host_seq_cached[b] + 1
-                    max_len = max(max_len, length)
-                    pairs += -(-length // 128)
+                    lengths.append(self.host_seq_cached[b] + 1)
             n = len(req)
             if n == 0:
                 self._singles = SingleTokens(None, None, 0, 0)
             else:
                 packed = torch.tensor(req + tok, dtype=torch.int32).to(self.device)
-                self._singles = SingleTokens(packed[:n], packed[n:], n, max_len, pairs)
+                self._singles = SingleTokens(packed[:n], packed[n:], n, max(lengths), lengths)
         return self._singles
 
 

@@ -59,8 +59,10 @@ class GQAAttention(Mixer):
         p = self.params
         self.ops = ops
         dt = ops.act_dtype
-        wq = interleave_rope_rows(tensors["wq"], p.n_heads)
-        wk = interleave_rope_rows(tensors["wk"], p.n_kv_heads)
+        wq, wk = tensors["wq"], tensors["wk"]
+        if p.qk_layout == "half_split":
+            wq = interleave_rope_rows(wq, p.n_heads)
+            wk = interleave_rope_rows(wk, p.n_kv_heads)
         self.wqkv = torch.cat([wq, wk, tensors["wv"]], dim=0).to(dt).contiguous()
         self.wo = tensors["wo"].to(dt).contiguous()
         self.freqs = self.position.table(ops.device)

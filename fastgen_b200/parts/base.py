@@ -36,11 +36,26 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """What a mixer that caches per-token keys and values needs per token."""
+    """What a mixer that caches per-token entries needs per token.
+
+    The usual case is keys and values: two pools of ``[pages, n_kv_heads, page, head_dim]``.
+    ``n_pools = 1`` asks for one pool only (a mixer that keeps one entry per token, say a
+    compressed one from which it makes keys and values itself); ``page_size`` asks for pages
+    of that many tokens instead of the engine's.  Runs with equal specs share a group of
+    pages; every group has its own pool of page ids and its own block table per request.
+    """
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # keys a query may see, itself included
+    n_pools: int = 2  # 2: keys and values; 1: one entry per token
+    page_size: Optional[int] = None  # tokens per page; None: the engine's page size
+
+    def __post_init__(self) -> None:
+        if self.n_pools not in (1, 2):
+            raise ValueError(f"a cache spec asks for 1 or 2 pools, got {self.n_pools}")
+        if self.page_size is not None and self.page_size <= 0:
+            raise ValueError(f"page size must be positive, got {self.page_size}")
 
 
 @dataclass(frozen=True)
@@ -124,14 +139,16 @@ class FeedForward(Part):
 class Block:
     """Arrangement of a layer's parts around the residual stream."""
 
-    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm):
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm, **extra: Part):
         self.mixer = mixer
         self.mixer_norm = mixer_norm
         self.ffn = ffn
         self.ffn_norm = ffn_norm
+        #: further parts by name (``LayerSpec.extra``), for arrangements with more than four
+        self.extra: Dict[str, Part] = dict(extra)
 
     def parts(self) -> Sequence[Part]:
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, *self.extra.values())
 
     def forward(self, h, pending, ctx, memory):
         """Run the layer.  ``h`` is the residual stream [T, dim] (float32) and
@@ -192,8 +209,8 @@ def make_position(spec: PartSpec) -> PositionEncoding:
     return _make(_POSITIONS, "position encoding", spec)
 
 
-def make_block(kind: str, mixer, mixer_norm, ffn, ffn_norm) -> Block:
+def make_block(kind: str, mixer, mixer_norm, ffn, ffn_norm, **extra) -> Block:
     factory = _BLOCKS.get(kind)
     if factory is None:
         raise KeyError(f"no block of kind {kind!r} is registered; known: {sorted(_BLOCKS)}")
-    return factory(mixer, mixer_norm, ffn, ffn_norm)
+    return factory(mixer, mixer_norm, ffn, ffn_norm, **extra)

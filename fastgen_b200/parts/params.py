@@ -41,7 +41,12 @@ class AttentionParams:
 
     ``window`` is the number of most recent keys a query may see (itself
     included); ``None`` means all of them.  ``position`` is a ``PartSpec`` of a
-    position encoding applied to queries and keys.
+    position encoding applied to queries and keys.  ``qk_layout`` says how the
+    checkpoint orders the rows of a head in its query and key projections:
+    ``"half_split"`` (the rotated pair of row ``j`` is row ``j + head_dim/2``, as
+    Hugging Face Llama checkpoints store them; the rows are reordered at bind time,
+    fastgen/utils/loading.py:296-305) or ``"adjacent"`` (pairs ``(2j, 2j+1)``, what the
+    kernels rotate: taken as stored).
     """
 
     dim: int
@@ -51,8 +56,11 @@ class AttentionParams:
     position: object
     window: Optional[int] = None
     softmax_scale: Optional[float] = None  # None: head_dim ** -0.5 (forward.py:221)
+    qk_layout: str = "adjacent"
 
     def __post_init__(self) -> None:
+        if self.qk_layout not in ("adjacent", "half_split"):
+            raise ValueError(f"qk_layout must be 'adjacent' or 'half_split', got {self.qk_layout!r}")
         if self.n_heads % self.n_kv_heads != 0:
             raise ValueError(
                 f"{self.n_heads} query heads cannot be grouped over "

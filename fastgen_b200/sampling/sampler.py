@@ -39,16 +39,20 @@ class Sampler:
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], keys: Sequence[int],
                positions: Sequence[int]) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Sample one token per row of ``logits`` [rows, vocab].  Returns device
-        tensors (tokens int32, logprobs float32 or ``None``)."""
+        tensors (int32 ``[rows + 1]``: the tokens, then the device status word as the
+        step's kernels left it; logprobs float32 ``[rows]`` or ``None``).  The status
+        word comes with the tokens so that the caller's one read of them also tells it
+        whether a kernel recorded a fault (``csrc.ops.describe_status``)."""
         rows = logits.shape[0]
         dev = self.ops.device
-        out = torch.empty(rows, dtype=torch.int32, device=dev)
+        out = torch.empty(rows + 1, dtype=torch.int32, device=dev)
         lp = torch.empty(rows, dtype=torch.float32, device=dev) if self.logprobs else None
         if self.use_sampling and any(t > 0 for t in temperatures):
             temps = torch.tensor(list(temperatures), dtype=torch.float32).to(dev)
             kk = torch.tensor(list(keys), dtype=torch.int64).to(dev)
             pp = torch.tensor(list(positions), dtype=torch.int32).to(dev)
-            self.ops.sample(logits, temps, self.top_p, self.seed, kk, pp, out, lp, self._scratch_for(rows))
+            self.ops.sample(logits, temps, self.top_p, self.seed, kk, pp, out, lp, self._scratch_for(rows),
+                            with_status=True)
         else:
-            self.ops.sample(logits, None, 1.0, self.seed, None, None, out, lp, None)
+            self.ops.sample(logits, None, 1.0, self.seed, None, None, out, lp, None, with_status=True)
         return out, lp

@@ -91,7 +91,7 @@ def main(argv=None) -> int:
     print("---")
 
     dialog: List[dict] = []
-    history: List[int] = []
+    turns: List[List[int]] = []  # token-id mode: the conversation so far, a list per message
     while True:
         rnd = 1 + len(dialog) // 2
         try:
@@ -105,7 +105,7 @@ def main(argv=None) -> int:
             try:
                 n = int(msg[2:].strip())
                 dialog = dialog[: 2 * (n - 1)]
-                history = []
+                turns = turns[: 2 * (n - 1)]
             except ValueError:
                 print("invalid command")
             continue
@@ -122,11 +122,16 @@ def main(argv=None) -> int:
             tokens = tokenizer.encode_dialog(dialog)
         else:
             try:
-                tokens = [int(t) for t in msg.replace(",", " ").split()]
+                ids = [int(t) for t in msg.replace(",", " ").split()]
             except ValueError:
                 print("invalid token ids")
                 continue
+            if not ids:
+                continue
             dialog.append(dict(role="user", content=msg))
+            turns.append(ids)
+            # the conversation goes in whole, as a chat template would render it
+            tokens = [t for turn in turns for t in turn]
         if not tokens:
             dialog.pop()
             continue
@@ -137,6 +142,8 @@ def main(argv=None) -> int:
         if pkt.error:
             print(f"error: {pkt.error}")
             dialog.pop()
+            if tokenizer is None:
+                turns.pop()
             continue
         ntoks = len(pkt.tokens)
         out = list(pkt.tokens)
@@ -144,6 +151,8 @@ def main(argv=None) -> int:
             out = out[:-1]
         text = tokenizer.decode(out) if tokenizer is not None else " ".join(map(str, out))
         dialog.append(dict(role="assistant", content=text))
+        if tokenizer is None:
+            turns.append(out)
         print(text)
         print(f"--- [{ntoks} tokens, {tps:.3f}toks/s]")
 

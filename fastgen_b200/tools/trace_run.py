@@ -19,7 +19,7 @@ def main(argv=None) -> int:
         "--max-tokens", type=int, required=True,
         help="most tokens live requests hold at any time (each rounded up to whole pages)",
     )
-    parser.add_argument("--page-size", type=int, default=64, help="tokens per cache page (at most 64)")
+    parser.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
     parser.add_argument("--max-requests", type=int, default=4, help="most requests live at a time")
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
@@ -28,14 +28,17 @@ def main(argv=None) -> int:
 
     from ..engine import Engine, Model, StepEntry
 
-    if not 0 < args.page_size <= 64:
-        parser.error("--page-size must be between 1 and 64")
+    if args.page_size <= 0:
+        parser.error("--page-size must be positive")
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
 
     model = Model.load(args.model, dtype, args.device)
-    n_pages = max(1, -(-args.max_tokens // args.page_size))
+    # --max-tokens counts every live request rounded up to a multiple of 64; pages that do
+    # not divide 64 (larger ones above all) may need up to one page more a live request
+    slack = 0 if 64 % args.page_size == 0 else args.max_requests * args.page_size
+    n_pages = max(1, -(-(args.max_tokens + slack) // args.page_size))
     engine = Engine(
         model,
         page_size=args.page_size,

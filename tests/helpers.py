@@ -179,14 +179,51 @@ def collect(steps, outputs: Dict[int, np.ndarray]) -> Dict[str, Dict[int, np.nda
     return got
 
 
-def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_requests: int = 4):
-    """Replay ``steps`` through the package's engine in this process."""
+def plan_many(requests: Dict[str, List[int]], seed: int, max_live: int = 14, admit_per_step: int = 3,
+              decode_tail: int = 40):
+    """Many live requests: a few are admitted a step, each with its prompt (whole, or in
+    two portions) beside the single tokens of those that are already decoding; once all
+    are in, steps of single tokens only, with requests ending one after another, so the
+    number of live requests walks down through every batch size."""
+    rng = random.Random(seed)
+    waiting = list(requests.items())
+    live: Dict[str, Dict] = {}
+    steps, n = [], 0
+    while waiting or live:
+        admitted = 0
+        while waiting and len(live) < max_live and admitted < admit_per_step:
+            rid, toks = waiting.pop(0)
+            live[rid] = dict(toks=toks, p=0, prompt=max(1, len(toks) - rng.randrange(4, decode_tail)))
+            admitted += 1
+        entries, end = [], []
+        for rid, st in list(live.items()):
+            left = st["prompt"] - st["p"]
+            if left > 0:
+                m = left if left < 40 or rng.random() < 0.5 else left // 2
+            else:
+                m = 1
+            toks = st["toks"][st["p"]:st["p"] + m]
+            entries.append(dict(id=rid, tokens=toks, want=list(range(m))))
+            st["p"] += m
+            if st["p"] == len(st["toks"]):
+                end.append(rid)
+                del live[rid]
+        steps.append(dict(step=n, entries=entries, end=end))
+        n += 1
+    return steps
+
+
+def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_requests: int = 4,
+               num_cuda_graphs: int = 16, before_step=None):
+    """Replay ``steps`` through the package's engine in this process.  ``before_step(engine,
+    step)`` runs before each step, after the requests it brings have been admitted."""
     from fastgen_b200.engine import Engine, Model, StepEntry
 
     model = Model.load(model_dir, dtype, "cuda:0")
     n_pages = max(1, -(-max_tokens // page_size))
     engine = Engine(model, page_size=page_size, n_pages=n_pages, max_requests=max_requests,
-                    max_length=min(model.args.max_positions, n_pages * page_size))
+                    max_length=min(model.args.max_positions, n_pages * page_size),
+                    num_cuda_graphs=num_cuda_graphs)
     outputs, live = {}, set()
     for st in steps:
         entries = []
@@ -195,6 +232,8 @@ def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_req
                 engine.admit(e["id"])
                 live.add(e["id"])
             entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
+        if before_step is not None:
+            before_step(engine, st)
         logits = engine.step(entries)
         if logits is not None:
             outputs[st["step"]] = logits.float().cpu().numpy()
@@ -206,23 +245,45 @@ def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_req
     return outputs, engine
 
 
+# The bfloat16 rule.  The plain implementation reads the same bfloat16 weights and computes in
+# float64; the engine rounds every activation to bfloat16 (2^-9 relative, about 0.1% rms) a
+# dozen times a layer, and the roundings add up like a random walk.  A row of logits may differ
+# from the plain one by BF16_L2 of the row's l2 norm and, in its worst entry, by BF16_MAX of the
+# row's largest logit.  The constants are about twice the worst ratios that the tests have
+# shown (they are printed at the end of a run: ``worst bfloat16 ratios``); the negative controls
+# of test_replay_gpu.py show that a single wrong page breaks them.
+BF16_L2 = 0.02
+BF16_MAX = 0.03
+worst_ratios = {"l2": 0.0, "max": 0.0, "rows": 0}
+
+
+def check_row(row: np.ndarray, ref: np.ndarray, dtype, what="") -> float:
+    """Hold one row of logits to the plain implementation's.  Returns the largest error."""
+    err = float(np.abs(row - ref).max())
+    if dtype == torch.float32:
+        assert err <= 1e-4, f"{what}: max abs err {err:.3e}"
+        top = np.sort(ref)[-2:]
+        if top[1] - top[0] > 2e-4:
+            assert int(row.argmax()) == int(ref.argmax()), f"{what}: argmax differs"
+        return err
+    l2 = float(np.linalg.norm(row - ref) / max(np.linalg.norm(ref), 1e-30))
+    mx = err / max(float(np.abs(ref).max()), 1e-30)
+    worst_ratios["l2"] = max(worst_ratios["l2"], l2)
+    worst_ratios["max"] = max(worst_ratios["max"], mx)
+    worst_ratios["rows"] += 1
+    assert l2 <= BF16_L2, f"{what}: l2 error {l2:.4f} of the row's norm (allowed {BF16_L2})"
+    assert mx <= BF16_MAX, f"{what}: worst entry off by {mx:.4f} of the largest logit (allowed {BF16_MAX})"
+    return err
+
+
 def compare(model_dir, requests, got, dtype) -> float:
     """Compare every collected row with the plain implementation; return the
     largest absolute error.  float32 must agree to 1e-4 with the same argmax;
-    bfloat16 within 2% of the logits' range (see tolerance notes in the tests)."""
+    bfloat16 under the rule of ``check_row``."""
     worst = 0.0
     for rid, toks in requests.items():
         ref = plain_logits(model_dir, toks)
         assert set(got[rid]) == set(range(len(toks))), f"{rid}: positions missing"
         for p, row in got[rid].items():
-            err = float(np.abs(row - ref[p]).max())
-            worst = max(worst, err)
-            if dtype == torch.float32:
-                assert err <= 1e-4, f"{rid} pos {p}: max abs err {err:.3e}"
-                top = np.sort(ref[p])[-2:]
-                if top[1] - top[0] > 2e-4:
-                    assert int(row.argmax()) == int(ref[p].argmax()), f"{rid} pos {p}: argmax differs"
-            else:
-                scale = float(np.abs(ref[p]).max())
-                assert err <= 0.02 * max(scale, 1.0), f"{rid} pos {p}: err {err:.3e} vs scale {scale:.3e}"
+            worst = max(worst, check_row(row, ref[p], dtype, f"{rid} pos {p}"))
     return worst

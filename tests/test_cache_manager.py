@@ -137,3 +137,33 @@ def test_random_orders_keep_invariants(seed):
     m.check()
     assert all(f == g.pool.n_pages for f, g in zip(m.free_pages(), m.groups))
     assert m.free_slots() == 4
+
+
+def test_groups_with_pages_of_their_own_and_one_pool():
+    """A spec may ask for its own page size and for a single pool: such runs form a group with its
+    own page ids, block-table width and byte count; one ``n_pages`` gives every group the same tokens."""
+    kv = CacheSpec(2, 16, None)
+    latent = CacheSpec(1, 12, None, n_pools=1, page_size=4)
+    windowed = CacheSpec(2, 16, 10, page_size=2)
+    m = CacheManager([kv, latent, kv, windowed], [None] * 4, [None] * 4, page_size=8, n_pages=6, max_requests=3,
+                     max_length=48)
+    assert [g.page_size for g in m.groups] == [8, 4, 2]
+    assert [g.pool.n_pages for g in m.groups] == [6, 12, 24]
+    assert [g.table_width for g in m.groups] == [6, 12, 24]
+    assert [g.bytes_per_token(2) for g in m.groups] == [2 * 2 * 2 * 16 * 2, 1 * 1 * 1 * 12 * 2, 2 * 1 * 2 * 16 * 2]
+    assert m.memory(1).page_size == 4 and m.memory(0).page_size == 8
+    r = m.admit("a")
+    assert m.pages_needed(r, 9) == [2, 3, 5]
+    m.reserve(r, 9)
+    m.advance(r, 9)
+    m.check()
+    m.reserve(r, 30)
+    m.advance(r, 30)
+    # the windowed group gave back what the window (10 keys) has passed, in pages of 2
+    assert m.free_pages() == [6 - 4, 12 - 8, 24 - 5]
+    m.check()
+    assert m.can_ever_hold(48) and not m.can_ever_hold(49)
+    m.release("a")
+    assert m.free_pages() == [6, 12, 24]
+    with pytest.raises(ValueError):
+        CacheSpec(1, 8, None, n_pools=3)

@@ -254,34 +254,15 @@ def test_rope_kv_write(ops32, dtype, hq, hkv, hd, page):
         ops32.check_status()
 
 
-@pytest.mark.skipif(os.environ.get("FG_STREAM_GEMM", "off") == "off",
-                    reason="the tcgen05 weight-streaming product is opt-in (FG_STREAM_GEMM=auto|all) and so is its test")
-@pytest.mark.parametrize("m,n,k", [(16, 128, 64), (9, 4096, 4096), (33, 1000, 200), (64, 6144, 4096),
-                                   (100, 28672, 4096), (64, 4096, 14336), (128, 331, 72), (256, 2048, 512)])
-def test_linear_stream(ops16, m, n, k):
-    """The tcgen05 weight-streaming product: tiles that fall to one block, tiles split over
-    several blocks (partial sums through scratch), sizes that are no multiple of the tile."""
-    g = torch.Generator().manual_seed(m + n + k)
-    x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
-    w = (torch.randn(n, k, generator=g) * 0.05).to(DEV, torch.bfloat16)
-    ref = x.double() @ w.double().t()
-    for out_dtype in (torch.bfloat16, torch.float32):
-        y = ops16.linear_stream(x, w, out_dtype=out_dtype)
-        ops16.check_status()
-        tol = float(ref.abs().max()) * (2.0 ** -7 if out_dtype == torch.bfloat16 else 1e-5) + 1e-3
-        assert float((y.double() - ref).abs().max()) <= tol
-    again = ops16.linear_stream(x, w, out_dtype=torch.float32)  # the arrival counts are back at zero
-    assert torch.equal(again, y)
-    # a token's result does not depend on the batch it is in
-    alone = ops16.linear_stream(x[:9].contiguous(), w, out_dtype=torch.float32)
-    assert torch.equal(alone, y[:9])
-
-
 # ---------------------------------------------------------------------------------
 # attention: a step context by hand, a paged cache with shuffled pages
 # ---------------------------------------------------------------------------------
-def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None, use_tma=True):
-    """seqs: list of (cached, new) per request.  Returns (out, ref) for the new tokens."""
+def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None, use_tma=True, runs=1, layer=0,
+                    pad_lanes=0):
+    """seqs: list of (cached, new) per request.  Returns (out, ref) for the new tokens.
+    ``runs``/``layer``: the pools hold ``runs`` layers (the others full of NaN) and the case
+    lives in layer ``layer``.  ``pad_lanes``: that many single-token lanes of slot -1 are
+    mixed in (a graph bucket larger than the step); their outputs are not compared."""
     from fastgen_b200.engine.step import StepContext
 
     dtype = ops.act_dtype
@@ -290,13 +271,17 @@ def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None, use_
     width = max(-(-t // page) for t in total) + 1
     n_pages = sum(-(-t // page) for t in total) + 3
     perm = torch.randperm(n_pages, generator=g).tolist()
-    kp = torch.randn(n_pages, hkv, page, hd, generator=g).to(DEV, dtype)  # garbage in unused slots
-    vp = torch.randn(n_pages, hkv, page, hd, generator=g).to(DEV, dtype)
+    kpool = torch.full((runs, n_pages, hkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    vpool = torch.full((runs, n_pages, hkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    kpool[layer] = torch.randn(n_pages, hkv, page, hd, generator=g).to(DEV, dtype)  # garbage in unused slots
+    vpool[layer] = torch.randn(n_pages, hkv, page, hd, generator=g).to(DEV, dtype)
+    kp, vp = kpool[layer], vpool[layer]
     table = torch.full((len(seqs) + 2, width), -1, dtype=torch.int32)
     ctx = StepContext(DEV)
-    qs, refs, pos, req = [], [], [], []
+    qs, refs, pos, req, keep = [], [], [], [], []
     slots = list(range(len(seqs) + 2))
     random.Random(seed).shuffle(slots)
+    pad_after = set(random.Random(seed + 1).sample(range(len(seqs)), min(pad_lanes, len(seqs))))
     for b, (cached, new) in enumerate(seqs):
         slot = slots[b]
         t = cached + new
@@ -317,9 +302,15 @@ def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None, use_
         ref = pl.causal_attention(q.double(), k.double(), v.double(), hd ** -0.5, window)[cached:]
         refs.append(ref.reshape(new, hq * hd))
         qs.append(q[cached:].reshape(new, hq * hd))
-        pos += list(range(cached, t)); req += [slot] * new
+        pos += list(range(cached, t)); req += [slot] * new; keep += [True] * new
         ctx.host_seq_slot.append(slot); ctx.host_seq_cached.append(cached)
         ctx.host_seq_start.append(ctx.host_seq_start[-1] + new)
+        if b in pad_after:
+            # a padding lane as a graph bucket has them: slot -1, position 0, some query
+            qs.append(torch.randn(1, hq * hd, generator=g).to(dtype))
+            pos.append(0); req.append(-1); keep.append(False)
+            ctx.host_seq_slot.append(-1); ctx.host_seq_cached.append(0)
+            ctx.host_seq_start.append(ctx.host_seq_start[-1] + 1)
     ctx.pos = torch.tensor(pos, dtype=torch.int32, device=DEV)
     ctx.req = torch.tensor(req, dtype=torch.int32, device=DEV)
     ctx.n_tokens = len(pos)
@@ -331,10 +322,12 @@ def _attention_case(ops, seqs, hq, hkv, hd, page, window, seed, boost=None, use_
     from fastgen_b200.cache import LayerMemory
     mem = LayerMemory(k_pages=kp, v_pages=vp, block_table=table.to(DEV), page_size=page)
     if use_tma:
-        mem.tensor_maps = ops.make_kv_tensor_maps(kp[None], vp[None], page)
+        mem.tensor_maps = ops.make_kv_tensor_maps(kpool, vpool, page)
+        mem.layer_index = layer
     ops.attention(wide[:, : q.shape[1]], out, mem, ctx, hq, hkv, hd, window, hd ** -0.5)
     ops.check_status()
-    return out.double().cpu(), torch.cat(refs)
+    keep = torch.tensor(keep)
+    return out.double().cpu()[keep], torch.cat(refs)
 
 
 CASES = [
@@ -381,6 +374,69 @@ def test_attention(ops32, ops16, case):
         assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), (use_tma, tc5, float((out - ref).abs().max()))
 
 
+@pytest.mark.parametrize("case", [3, 4, 8, 13, 14, 15, 16])
+def test_attention_in_a_later_layer_with_padding_lanes(ops32, ops16, case):
+    """The same cases in layer 2 of pools of 3 layers (the tiled loads' layer coordinate; the
+    other layers hold NaN), with lanes of slot -1 among the single tokens."""
+    seqs, hq, hkv, hd, page, window = CASES[case]
+    pads = min(3, sum(1 for _, n in seqs if n == 1))
+    out, ref = _attention_case(ops32, seqs, hq, hkv, hd, page, window, case, runs=3, layer=2, pad_lanes=pads)
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5), float((out - ref).abs().max())
+    for use_tma, tc5 in ((True, True), (True, False), (False, False)):
+        ops16.use_tcgen05 = tc5
+        try:
+            out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, case, use_tma=use_tma, runs=3,
+                                       layer=2, pad_lanes=pads)
+        finally:
+            ops16.use_tcgen05 = True
+        assert torch.allclose(out, ref, rtol=3e-2, atol=3e-2), (use_tma, tc5, float((out - ref).abs().max()))
+
+
+# One key among hundreds dominates the last query of every request (its score is 4 |q|^2 / sqrt(hd),
+# tens of units above the rest): a kernel that misses that key, or sees it when a window hides
+# it, is off by the size of a value, far beyond rounding.
+SHARP_TOL = 6e-2
+
+
+def _sharp(ops16, seqs, hq, hkv, hd, page, window, far, seed=77):
+    for use_tma, tc5 in ((True, True), (True, False), (False, False)):
+        ops16.use_tcgen05 = tc5
+        try:
+            out, ref = _attention_case(ops16, seqs, hq, hkv, hd, page, window, seed, boost=(None, far),
+                                       use_tma=use_tma, runs=2, layer=1)
+        finally:
+            ops16.use_tcgen05 = True
+        err = float((out - ref).abs().max())
+        assert err < SHARP_TOL, (use_tma, tc5, far, err)
+
+
+@pytest.mark.parametrize("hd,hq,hkv", [(64, 8, 2), (128, 8, 2), (128, 24, 2)])
+@pytest.mark.parametrize("page", [16, 64, 256])
+def test_attention_reaches_a_far_key_tiled(ops16, hd, hq, hkv, page):
+    """At the head sizes of the tiled-load kernels (tcgen05 and mma.sync prompts, the persistent and
+    the one-block-a-split single-token kernels; 24 heads over 2 is a group of 12, which the persistent
+    kernel does not take), the dominant key lies at 0, at the ends of key tiles, of splits and of pages."""
+    fars = sorted({0, 63, 64, 127, 128, page - 1, page, 2 * page - 1, 255, 256, 383})
+    singles = [(399 + i, 1) for i in range(13)]   # 13 requests: the persistent kernel where the group allows
+    for far in fars:
+        _sharp(ops16, [(0, 400)], hq, hkv, hd, page, None, far)
+        _sharp(ops16, [(250, 150)], hq, hkv, hd, page, None, far)
+        _sharp(ops16, singles, hq, hkv, hd, page, None, far)
+
+
+@pytest.mark.parametrize("hd,hq,hkv", [(64, 8, 2), (128, 4, 1), (128, 12, 1)])
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_window_edge_tiled(ops16, hd, hq, hkv, page):
+    """The key at pos - window must be out, the one at pos - window + 1 in: prompts (60, 40) and
+    (250, 150), single tokens alone and a dozen together."""
+    for window in (24, 100, 129):
+        for seqs in ([(60, 40)], [(250, 150)], [(399, 1)], [(399, 1)] * 12):
+            last = seqs[0][0] + seqs[0][1] - 1
+            for far in (last - window, last - window + 1):
+                if far >= 0:
+                    _sharp(ops16, seqs, hq, hkv, hd, page, window, far, seed=5)
+
+
 @pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
 def test_attention_reaches_a_far_key(ops32, ops16, far):
     """One key among hundreds dominates the last query: it must be found wherever it lies."""
@@ -421,6 +477,19 @@ def test_attention_missing_page_is_reported(ops16):
             ops16.check_status()
 
 
+def test_a_wait_that_runs_out_is_reported(ops16):
+    """The bounded wait of the kernels on a barrier nobody arrives at (a short limit): it
+    returns, the status word says so, the block's other waits are released at once, and a
+    wait on a completed phase is untouched."""
+    from fastgen_b200.csrc.ops import KernelError
+    first, second, cycles_first, cycles_second, completed = ops16.wait_timeout_selftest(limit=4096)
+    assert first == 0 and second == 0 and completed == 1
+    assert 0 < cycles_second < cycles_first / 8, (cycles_first, cycles_second)
+    with pytest.raises(KernelError, match="a bounded wait inside a kernel gave up"):
+        ops16.check_status()
+    ops16.check_status()  # the word is clear again
+
+
 # ---------------------------------------------------------------------------------
 # sampling
 # ---------------------------------------------------------------------------------
@@ -432,6 +501,12 @@ def test_argmax_and_logprobs(ops32):
         out = torch.empty(7, dtype=torch.int32, device=DEV)
         lp = torch.empty(7, dtype=torch.float32, device=DEV)
         ops32.sample(logits, None, 1.0, 0, None, None, out, lp, None)
+        # the status word rides along when asked for
+        out1 = torch.full((8,), -5, dtype=torch.int32, device=DEV)
+        ops32.status.fill_(6)
+        ops32.sample(logits, None, 1.0, 0, None, None, out1, None, None, with_status=True)
+        ops32.status.zero_()
+        assert torch.equal(out1[:7], out) and int(out1[7]) == 6
         ref = logits.argmax(-1)
         assert out[2] == vocab // 2
         keep = [0, 1, 3, 4, 5, 6]

@@ -52,10 +52,70 @@ def test_replay(tmp_path, name, dtype, plan):
     assert all(f == g.pool.n_pages for f, g in zip(engine.cache.free_pages(), engine.cache.groups))
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(tmp_path, dtype):
-    """The same through bin/trace_run, as a user runs it."""
-    name = "tiny_b"
+MANY = {"tiny_b": [30, 120, 75, 260, 41, 33, 180, 90, 64, 129, 200, 57, 310, 48, 150, 99],
+        "tiny_d": [70, 300, 131, 420, 45, 260, 129, 64, 390, 200, 88, 333, 150, 257, 40, 512],
+        "tiny_e": [50, 150, 260, 64, 129, 400, 33, 300, 210, 101, 99, 380, 45, 128, 256, 170]}
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(MANY))
+def test_replay_many_live_requests_in_padded_graphs(tmp_path, name, dtype):
+    """Up to 14 live requests and 3 graph buckets (1, 8, 14): most steps of single tokens
+    replay a graph with more lanes than requests (lanes of slot -1), and with more than 8
+    tokens a step bfloat16 takes the library product, the separate rotation and the separate
+    gate.  Lengths cross several splits of 128 keys; the pool has three pages to spare, so
+    pages are reused while others stay free."""
+    model_dir = H.make_model_dir(tmp_path, name)
+    reqs = _requests(name, MANY[name], 500)
+    page = PAGES[name]
+    steps = H.plan_many(reqs, seed=7, max_live=14)
+    assert max(len(st["entries"]) for st in steps) == 14
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page, H.max_live_tokens(steps, page) + 3 * page,
+                                   max_requests=14, num_cuda_graphs=3)
+    assert engine.graphs is not None and sorted(engine.graphs.buckets) == [1, 8, 14]
+    assert engine.graphs.padded_replays >= 10
+    got = H.collect(steps, outputs)
+    H.compare(model_dir, reqs, got, dtype)
+    assert engine.cache.n_live == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_d"])
+def test_a_wrong_page_breaks_the_comparison(tmp_path, name, dtype):
+    """The negative control of the comparisons: the mixed replay with ONE block-table entry of
+    one live request pointing at another request's page, for one step, must not pass."""
+    model_dir = H.make_model_dir(tmp_path, name)
+    reqs = _requests(name, LENGTHS[name] + [48, 17, 80], 200)
+    page = PAGES[name]
+    steps = H.plan_mixed(reqs, seed=5)
+    done = []
+
+    def swap_one_entry(engine, st):
+        if done or len(engine.cache._requests) < 2:
+            return
+        engine.cache.flush_tables()
+        a, b = list(engine.cache._requests.values())[:2]
+        grp = engine.cache.groups[0]
+        if not a.pages[0] or not b.pages[0] or a.length < page or all(e["id"] != a.request_id for e in st["entries"]):
+            return
+        # request a's first page becomes request b's first page on the device, for this step
+        lp_a, lp_b = min(a.pages[0]), min(b.pages[0])
+        grp.device_table[a.slot, lp_a] = int(b.pages[0][lp_b])
+        grp.dirty.append((a.slot, lp_a, a.pages[0][lp_a]))  # the next flush puts the right page back
+        done.append(st["step"])
+
+    outputs, _ = H.run_engine(model_dir, dtype, steps, page, H.max_live_tokens(steps, page), before_step=swap_one_entry)
+    assert done, "the control never swapped a page"
+    got = H.collect(steps, outputs)
+    with pytest.raises(AssertionError):
+        H.compare(model_dir, reqs, got, dtype)
+
+
+@pytest.mark.parametrize("dtype,name,page", [("float32", "tiny_b", None), ("bfloat16", "tiny_b", None),
+                                             ("bfloat16", "tiny_d", 256), ("float32", "tiny_d", 48)])
+def test_trace_run_program(tmp_path, dtype, name, page):
+    """The same through bin/trace_run, as a user runs it: with its default page, with pages of
+    256 tokens and with pages that do not divide 64 (--max-tokens still counts in 64s)."""
     model_dir = H.make_model_dir(tmp_path, name)
     reqs = _requests(name, [9, 40, 100, 64, 33], 300)
     steps = H.plan_mixed(reqs, seed=11)
@@ -63,7 +123,8 @@ def test_trace_run_program(tmp_path, dtype):
     root = Path(__file__).resolve().parent.parent
     proc = subprocess.run(
         [sys.executable, str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
-         "--out", str(out), "--max-tokens", str(H.max_live_tokens(steps, 64))],
+         "--out", str(out), "--max-tokens", str(H.max_live_tokens(steps, 64))]
+        + (["--page-size", str(page)] if page else []),
         input="".join(json.dumps(s) + "\n" for s in steps), text=True, capture_output=True, timeout=900,
     )
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -77,15 +138,18 @@ def test_trace_run_program(tmp_path, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 @pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
-def test_nothing_is_written_outside_the_fed_positions(tmp_path, name, dtype):
+@pytest.mark.parametrize("max_requests,num_graphs", [(3, 16), (12, 3)], ids=["exact", "padded"])
+def test_nothing_is_written_outside_the_fed_positions(tmp_path, name, dtype, max_requests, num_graphs):
     """Every slot of every page starts as a sentinel; after a prompt in portions and some
-    single tokens (captured graphs with padding lanes included), only the slots of the
-    request's own positions have changed, in its own pages."""
+    single tokens, only the slots of the request's own positions have changed, in its own
+    pages.  "padded": 12 slots and 3 graph buckets (1, 6, 12), so the steps of two single
+    tokens replay the graph of 6 lanes, four of them padding (slot -1)."""
     from fastgen_b200.engine import Engine, Model, StepEntry
 
     model = Model.load(H.make_model_dir(tmp_path, name), dtype, "cuda:0")
     page = PAGES[name]
-    engine = Engine(model, page_size=page, n_pages=12, max_requests=3, max_length=12 * page)
+    engine = Engine(model, page_size=page, n_pages=12, max_requests=max_requests, max_length=12 * page,
+                    num_cuda_graphs=num_graphs)
     sentinel = 12345.0
     for grp in engine.cache.groups:
         grp.k_pages.fill_(sentinel)
@@ -97,17 +161,30 @@ def test_nothing_is_written_outside_the_fed_positions(tmp_path, name, dtype):
     cut = page + 3
     engine.step([StepEntry("a", toks[:cut], [])])
     engine.step([StepEntry("a", toks[cut:-4], [len(toks) - 4 - cut - 1])])
-    for t in toks[-4:]:
-        engine.step([StepEntry("a", [t], [0])])
+    padded = max_requests > 3
+    other = H.random_tokens(vocab, page + 6, 9)
+    if padded:
+        engine.admit("b")
+        engine.step([StepEntry("b", other[:-4], [])])
+    for i, t in enumerate(toks[-4:]):
+        entries = [StepEntry("a", [t], [0])]
+        if padded:
+            entries.append(StepEntry("b", [other[len(other) - 4 + i]], [0]))
+        engine.step(entries)
     engine.ops.check_status()
-    req = engine.cache.get("a")
-    assert req.length == len(toks)
+    if padded:
+        assert sorted(engine.graphs.buckets) == [6] and engine.graphs.padded_replays == 4
+    lengths = {"a": len(toks), "b": len(other)} if padded else {"a": len(toks)}
     for gi, grp in enumerate(engine.cache.groups):
-        own = req.pages[gi]
+        owner = {}
+        for rid, n in lengths.items():
+            req = engine.cache.get(rid)
+            assert req.length == n
+            for lp, pg in req.pages[gi].items():
+                owner[pg] = (lp, n)
         for pool in (grp.k_pages, grp.v_pages):  # [runs, pages, kv heads, page, head_dim]
             touched = (pool != sentinel).any(-1).any(2).any(0).cpu()  # [pages, page]
             for pg in range(pool.shape[1]):
-                logical = [lp for lp, p in own.items() if p == pg]
                 for slot in range(page):
-                    expect = bool(logical) and logical[0] * page + slot < len(toks)
+                    expect = pg in owner and owner[pg][0] * page + slot < owner[pg][1]
                     assert bool(touched[pg, slot]) == expect, (gi, pg, slot)

@@ -48,8 +48,7 @@ def test_every_declared_signature_belongs_to_its_library():
     called = set(re.findall(r"\blib\.(fg_\w+)\(", Path(ops.__file__).read_text()))
     undeclared = called - set(ops._CORE_SIGNATURES) - set(ops._ATTN_SIGNATURES)
     int_only = {"fg_attention_decode_scratch_floats", "fg_attention_decode_split", "fg_attention_prefill_rows",
-                "fg_attention_rows_per_block", "fg_gemm_stream_max_m", "fg_gemm_stream_scratch_floats",
-                "fg_last_error"}
+                "fg_attention_rows_per_block", "fg_last_error"}
     assert undeclared <= int_only, undeclared - int_only
 
 
