@@ -23,3 +23,6 @@ def pytest_terminal_summary(terminalreporter):
             f"worst bfloat16 ratios over {w['rows']} rows: l2 {w['l2']:.4f} (bound {helpers.BF16_L2}), "
             f"largest entry {w['max']:.4f} (bound {helpers.BF16_MAX})"
         )
+        top = sorted(helpers.worst_by_test.items(), key=lambda kv: -kv[1][0])[:8]
+        for name, (l2, mx) in top:
+            terminalreporter.write_line(f"  {l2:.4f} {mx:.4f}  {name}")

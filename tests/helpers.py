@@ -249,15 +249,21 @@ def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_req
 # float64; the engine rounds every activation to bfloat16 (2^-9 relative, about 0.1% rms) a
 # dozen times a layer, and the roundings add up like a random walk.  A row of logits may differ
 # from the plain one by BF16_L2 of the row's l2 norm and, in its worst entry, by BF16_MAX of the
-# row's largest logit.  The constants are about twice the worst ratios that the tests have
-# shown (they are printed at the end of a run: ``worst bfloat16 ratios``); the negative controls
-# of test_replay_gpu.py show that a single wrong page breaks them.
-BF16_L2 = 0.02
-BF16_MAX = 0.03
+# row's largest logit.  The constants are twice the worst ratios that the tests of the tiny
+# models have shown (0.0091 and 0.0103; every run prints its own at the end: ``worst bfloat16
+# ratios``); the negative controls of test_replay_gpu.py show that a single wrong page, for a
+# single step, breaks them.  At the widths of the 8B layers (sums over 4,096 and 14,336 terms)
+# the worst seen were 0.0157 and 0.0215, and that test passes ``wide=True`` for twice those.
+BF16_L2 = 0.018
+BF16_MAX = 0.021
+BF16_L2_WIDE = 0.03
+BF16_MAX_WIDE = 0.043
 worst_ratios = {"l2": 0.0, "max": 0.0, "rows": 0}
+worst_by_test: Dict[str, List[float]] = {}
+record_ratios = True  # negative controls switch this off: their errors are meant to be large
 
 
-def check_row(row: np.ndarray, ref: np.ndarray, dtype, what="") -> float:
+def check_row(row: np.ndarray, ref: np.ndarray, dtype, what="", wide: bool = False) -> float:
     """Hold one row of logits to the plain implementation's.  Returns the largest error."""
     err = float(np.abs(row - ref).max())
     if dtype == torch.float32:
@@ -268,11 +274,16 @@ def check_row(row: np.ndarray, ref: np.ndarray, dtype, what="") -> float:
         return err
     l2 = float(np.linalg.norm(row - ref) / max(np.linalg.norm(ref), 1e-30))
     mx = err / max(float(np.abs(ref).max()), 1e-30)
-    worst_ratios["l2"] = max(worst_ratios["l2"], l2)
-    worst_ratios["max"] = max(worst_ratios["max"], mx)
-    worst_ratios["rows"] += 1
-    assert l2 <= BF16_L2, f"{what}: l2 error {l2:.4f} of the row's norm (allowed {BF16_L2})"
-    assert mx <= BF16_MAX, f"{what}: worst entry off by {mx:.4f} of the largest logit (allowed {BF16_MAX})"
+    if record_ratios:
+        import os
+        worst_ratios["l2"] = max(worst_ratios["l2"], l2)
+        worst_ratios["max"] = max(worst_ratios["max"], mx)
+        worst_ratios["rows"] += 1
+        per = worst_by_test.setdefault(os.environ.get("PYTEST_CURRENT_TEST", "?").split(" ")[0], [0.0, 0.0])
+        per[0], per[1] = max(per[0], l2), max(per[1], mx)
+    bound_l2, bound_max = (BF16_L2_WIDE, BF16_MAX_WIDE) if wide else (BF16_L2, BF16_MAX)
+    assert l2 <= bound_l2, f"{what}: l2 error {l2:.4f} of the row's norm (allowed {bound_l2})"
+    assert mx <= bound_max, f"{what}: worst entry off by {mx:.4f} of the largest logit (allowed {bound_max})"
     return err
 
 

@@ -235,7 +235,8 @@ def test_fgchat_token_id_mode(tmp_path):
 def test_fgchat_token_id_mode_keeps_the_conversation(tmp_path):
     """The second round's prompt is the first prompt, the first answer and the new line; ``/r 2``
     goes back to the state before round 2."""
-    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    import re
+    model_dir = H.make_model_dir(tmp_path, "tiny_b", std=0.08)  # weights under which the history matters
     root = Path(__file__).resolve().parent.parent
     proc = subprocess.run(
         [sys.executable, str(root / "bin" / "fgchat"), str(model_dir), "--temperature", "0.0",
@@ -247,7 +248,9 @@ def test_fgchat_token_id_mode_keeps_the_conversation(tmp_path):
     first = pl.greedy(model, [5, 17, 3, 200], 5)
     second = pl.greedy(model, [5, 17, 3, 200] + first + [9, 9, 41], 5)
     again = pl.greedy(model, [5, 17, 3, 200] + first + [77, 1], 5)
-    answers = [l for l in proc.stdout.splitlines() if l and all(c.isdigit() or c == " " for c in l)]
+    assert second != pl.greedy(model, [9, 9, 41], 5) and again != pl.greedy(model, [77, 1], 5)
+    lines = [re.sub(r"^(\d+> )+", "", l) for l in proc.stdout.splitlines()]  # the prompts share the answers' lines
+    answers = [l for l in lines if l and all(c.isdigit() or c == " " for c in l)]
     assert answers == [" ".join(map(str, t)) for t in (first, second, again)], proc.stdout
 
 
@@ -306,11 +309,11 @@ def test_cache_size_from_the_memory_budget(tmp_path):
 
     model_dir = H.make_model_dir(tmp_path, "tiny_b")
     prompts = [H.random_tokens(320, n, 80 + i) for i, n in enumerate([9, 40])]
-    args = GenArgs(use_sampling=False, max_gen=8, cache_block=16, max_batch=4, gpu_gb=0.104, prefill_gb=0.1)
+    args = GenArgs(use_sampling=False, max_gen=8, cache_block=16, max_batch=4, gpu_gb=0.11, prefill_gb=0.1)
     assert args.max_seq < 0 and args.num_cuda_graphs == 16
     fg = Fastgen.build(HfLoader(model_dir), args, tp_mesh=None, device=torch.device("cuda:0"), dtype=torch.float32)
     per_token = 2 * 3 * 3 * 32 * 4  # keys and values, 3 layers, 3 heads of 32, float32
-    expect = (int(0.104e9) - fg.model.weight_bytes() - int(0.1e9)) // per_token
+    expect = (int(0.11e9) - fg.model.weight_bytes() - int(0.1e9)) // per_token
     expect = -(-expect // 16) * 16
     assert fg.max_seq == expect and 1000 < expect < 3000
     assert fg.engine.cache.groups[0].pool.n_pages == expect // 16

@@ -726,4 +726,4 @@ def test_8b_layer_shape(tmp_path, dtype):
     got = H.collect(steps, outputs)
     for rows, r in ((got["a"], ref), (got["b"], ref_other)):
         for p, row in rows.items():
-            H.check_row(row, r[p], dtype, f"pos {p}")
+            H.check_row(row, r[p], dtype, f"pos {p}", wide=True)

@@ -94,7 +94,9 @@ def test_plain_attention_matches_the_reference_on_the_device(tmp_path, name):
         return torch.tensor(t, dtype=torch.int32, device=dev)
 
     tbl = torch.tensor([[0, 1], [2, 3]], dtype=torch.int32, device=dev)
-    with torch.inference_mode():
+    # the reference makes its frequency table and index tensors on the default device; its own
+    # tools set that to the GPU (fastgen/tools/chat.py:47-48)
+    with torch.inference_mode(), torch.device(dev):
         # whole prompts of several lengths: scale, grouping of the heads, the causal mask
         for t in (1, 2, 63, 64, 65, 130, 300):
             logits = fwd.prefill(model, toks(a[:t]), [(0, t)], tbl[:1], PAGE, cache())
