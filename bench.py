@@ -136,7 +136,8 @@ def run_ours(args) -> dict:
     vocab = cfg["vocab_size"]
     ctx_len = args.context
     k, w = args.steps, args.warmup
-    prompt_len = max(1, ctx_len - k - w)
+    # the timed steps end at the context length, or (--from-position) start at that position
+    prompt_len = max(1, (args.from_position if args.from_position else ctx_len - k) - w)
     max_b = max(args.batch, 64 if not args.skip_points else args.batch, 1)
     n_pages = max_b * (-(-(ctx_len + 1) // PAGE)) + PREFILL_TOKENS // PAGE + 2
     engine = Engine(model, page_size=PAGE, n_pages=n_pages, max_requests=max_b,
@@ -227,7 +228,6 @@ def run_ours(args) -> dict:
         b.record()
         torch.cuda.synchronize()
         ms = a.elapsed_time(b)
-        clk = clocks.stop() if clocks else None
         launches = Ops.launches - launches0
         last_len = reqs[0].length
         engine.ops.check_status()
@@ -236,7 +236,7 @@ def run_ours(args) -> dict:
         avg_ctx = (first_len + last_len) / 2
         step_bytes = weight_bytes + batch * avg_ctx * kv_per_token
         return dict(ms_per_step=ms / steps, tok_s=batch * steps / ms * 1e3, launches=launches,
-                    gbs=step_bytes / (ms / steps * 1e-3) / 1e9, clocks=clk, first=first_len, last=last_len)
+                    gbs=step_bytes / (ms / steps * 1e-3) / 1e9, first=first_len, last=last_len)
 
     if args.skip_decode:
         print(json.dumps({"impl": "ours", "prefill": prefill, "note": "decode skipped"}))
@@ -244,25 +244,44 @@ def run_ours(args) -> dict:
     clocks = ClockSampler()
     main = decode_run(args.batch, k, w, clocks)
     # ---- the same through the Python entry point: host tokens in, host tokens out ----
+    # As the reference arm measures itself (baseline/reference_arm.py): the same prompts are
+    # generated twice, for `warmup` and for `warmup + n` new tokens, all prompts admitted and
+    # prefilled in one step, and the difference of the wall-clock times is divided into the
+    # difference of the generated tokens.  n is at least 200 decode steps of the full batch; every
+    # step's tokens come from pinned host memory and its sampled tokens are read back to the host.
     e2e = None
-    fg = None if args.skip_e2e else Fastgen(GenArgs(use_sampling=False, max_batch=args.batch, max_seq=args.batch * (ctx_len + PAGE),
-                         max_gen=k + w, cache_block=PAGE, max_prefill=PREFILL_TOKENS,
-                         num_cuda_graphs=args.batch), model, stop_tokens=[])
-    if fg is not None:
-        q = queue.Queue()
-        for i in range(args.batch):
-            q.put(Packet(thread_id=i, tokens=prompt(prompt_len)))
-        q.put(None)
-        n_out = sum(len(p.tokens) for p in fg.generate(q))
-        log = [s for s in fg.step_log if s["prompt_tokens"] == 0 and s["decode_tokens"] == args.batch]
-        tail = log[-k:] if len(log) > k else log[1:]
-        e2e_tokens = sum(s["decode_tokens"] for s in tail)
-        e2e_s = tail[-1]["t_end"] - tail[0]["t_start"]
-        e2e = dict(value=round(e2e_tokens / e2e_s, 1), unit="tokens/s",
-                   h2d_bytes_per_step=int(sum(s["h2d_bytes"] for s in tail) / len(tail)),
-                   d2h_bytes_per_step=int(sum(s["d2h_bytes"] for s in tail) / len(tail)),
-                   steps=len(tail), generated=n_out, host_sync_every_steps=fg.gen_args.sync_freq)
+    if not args.skip_e2e:
+        n_e2e = max(k, 200)
+        e2e_prompt = max(1, ctx_len - n_e2e - w)
+        fg = Fastgen(GenArgs(use_sampling=False, max_batch=args.batch, max_seq=args.batch * (ctx_len + PAGE),
+                             cache_block=PAGE, max_prefill=args.batch * ctx_len, num_cuda_graphs=args.batch),
+                     model, stop_tokens=[])
+        prompts = [prompt(e2e_prompt) for _ in range(args.batch)]
+
+        def generate(max_gen):
+            q = queue.Queue()
+            for i, p in enumerate(prompts):
+                q.put(Packet(thread_id=i, tokens=p, max_gen=max_gen))
+            q.put(None)
+            first = len(fg.step_log)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            n = sum(len(p.tokens) for p in fg.generate(q))
+            torch.cuda.synchronize()
+            return time.perf_counter() - t0, n, fg.step_log[first:]
+
+        generate(2)
+        t_short, n_short, _ = generate(w)
+        t_long, n_long, log = generate(w + n_e2e)
+        full = [s for s in log if s["prompt_tokens"] == 0 and s["decode_tokens"] == args.batch]
+        e2e = dict(value=round((n_long - n_short) / (t_long - t_short), 1), unit="tokens/s",
+                   h2d_bytes_per_step=int(sum(s["h2d_bytes"] for s in full) / max(1, len(full))),
+                   d2h_bytes_per_step=int(sum(s["d2h_bytes"] for s in full) / max(1, len(full))),
+                   steps=n_e2e, generated=n_long, full_batch_steps=len(full),
+                   wall_s=round(t_long - t_short, 4), host_sync_every_steps=fg.gen_args.sync_freq,
+                   method="wall clock of generate(): (tokens B - tokens A) / (time B - time A)")
         fg.destroy()
+    clk = clocks.stop()
 
     # ---- the other batch sizes (after the end-to-end run, which shares the main run's conditions) ----
     points = {}
@@ -287,7 +306,7 @@ def run_ours(args) -> dict:
         "points": points,
         "e2e": e2e,
         "gpu_launches": main["launches"],
-        "clocks": main["clocks"],
+        "clocks": clk,
     }
 
 
@@ -303,7 +322,11 @@ def run_reference(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed decode steps (default 256, or up to the context length with --from-position)")
+    ap.add_argument("--from-position", type=int, default=0,
+                    help="time the decode steps from this position on (e.g. 2048, with --context 4096: the "
+                         "steps span 2,048 -> 4,096); default: the steps end at the context length")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
@@ -320,6 +343,12 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.from_position and not 0 < args.from_position < args.context:
+        ap.error("--from-position must lie inside the context")
+    if args.steps is None:
+        args.steps = args.context - args.from_position if args.from_position else 256
+    if args.from_position and args.from_position + args.steps > args.context:
+        ap.error("--from-position + --steps goes beyond --context")
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(out))
     return 0
