@@ -17,6 +17,7 @@ import importlib.util
 import json
 import queue
 import sys
+import threading
 import time
 from pathlib import Path
 
@@ -35,6 +36,8 @@ def main() -> int:
     ap.add_argument("--shape", default="3b")
     ap.add_argument("--requests", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--arrive-over", type=float, default=None,
+                    help="seconds over which the requests arrive (0: all at once; default: the workload's own)")
     args = ap.parse_args()
     wl = _workloads()
     cfg = wl.config_of(args.shape, args.layers)
@@ -93,13 +96,30 @@ def main() -> int:
                            max_prefill=w["max_prefill"], min_prefill=min(2048, w["max_prefill"]))
         fg = Fastgen.build(RandomLoader(), gen_args, tp_mesh=None, device=device, profile_sig=None)
 
+        span = w["arrive_over"] if args.arrive_over is None else args.arrive_over
+        arrivals = wl.arrival_times(len(reqs), span, w["seed"]) if span > 0 else None
+
         def run(items):
             q = queue.Queue()
-            for i, (p, g) in enumerate(items):
-                q.put(Packet(thread_id=i, tokens=p, max_gen=g))
-            q.put(None)
+            packets = [Packet(thread_id=i, tokens=p, max_gen=g) for i, (p, g) in enumerate(items)]
+            producer = None
+            if arrivals is None:
+                for pkt in packets:
+                    q.put(pkt)
+                q.put(None)
+            else:  # the same seeded schedule as the other arm's
+                def produce(t_begin):
+                    for pkt, at in zip(packets, arrivals):
+                        delay = t_begin + at - time.perf_counter()
+                        if delay > 0:
+                            time.sleep(delay)
+                        q.put(pkt)
+                    q.put(None)
+                producer = threading.Thread(target=produce, args=(time.perf_counter(),), daemon=True)
             torch.cuda.synchronize()
             t0 = time.perf_counter()
+            if producer is not None:
+                producer.start()
             n_out = sum(len(pkt.tokens) for pkt in fg.generate(q))
             torch.cuda.synchronize()
             return time.perf_counter() - t0, n_out
@@ -119,7 +139,7 @@ def main() -> int:
         "layers": cfg["num_hidden_layers"], "prompt_tokens": n_prompt, "generated_tokens": n_out,
         "seconds": round(seconds, 3), "first_run_seconds": round(first_seconds, 3), "generated_tok_s": round(n_out / seconds, 1),
         "total_tok_s": round((n_out + n_prompt) / seconds, 1), "max_batch": max_batch,
-        "max_prefill": w["max_prefill"], "page": block,
+        "max_prefill": w["max_prefill"], "page": block, "arrive_over_s": span,
         "timing": "wall clock around generate(), host tokens in and out",
     }))
     return 0

@@ -177,7 +177,9 @@ class Fastgen:
             min_prefill=args.min_prefill, min_prefill_batch=args.min_prefill_batch,
         )
         self.steps = 0
-        self.step_log: List[dict] = []  # per step: times, token counts, bytes copied
+        # per step: host times, decoded and prompt tokens, bytes copied, cached positions read
+        # (kv_tokens) and (query, key) pairs of its attention (key_pairs)
+        self.step_log: List[dict] = []
         # a trace on request (generate.py:187-196, 364-403): FG_PROFILE_ITERS scheduler iterations
         # after ``request_profile()``, written as a chrome trace into FG_PROFILE_DIR
         self.profile_iters = int(os.environ.get("FG_PROFILE_ITERS", "8"))
@@ -316,12 +318,14 @@ class Fastgen:
             word |= row.pop()
         self.steps += n_steps
         t_end = time.perf_counter()
+        lengths = sum(h.length for h in handles)
         for k in range(n_steps):
             self.step_log.append(dict(
                 t_start=t_start + (t_end - t_start) * k / n_steps,
                 t_end=t_start + (t_end - t_start) * (k + 1) / n_steps,
                 decode_tokens=len(reqs), prompt_tokens=0,
                 h2d_bytes=engine.graphs.last_h2d_bytes, d2h_bytes=4 * (len(reqs) + 1),
+                kv_tokens=lengths + (k + 1) * len(reqs), key_pairs=lengths + (k + 1) * len(reqs),
             ))
         if word:
             yield from self._fail_step(reqs, word)
@@ -372,6 +376,12 @@ class Fastgen:
                 for e in plan
             ]
             t_start = time.perf_counter()
+            # cached positions the step reads, and (query, key) pairs its attention forms
+            kv_tokens = key_pairs = 0
+            for e in plan:
+                before, n = self.engine.cache.get(id(e.request)).length, len(e.tokens)
+                kv_tokens += before + n
+                key_pairs += n * before + n * (n + 1) // 2
             logits = self.engine.step_reserved(entries)
             self.steps += 1
             sampling = [e for e in plan if e.samples]
@@ -393,6 +403,7 @@ class Fastgen:
                 t_start=t_start, t_end=time.perf_counter(), decode_tokens=n_decode,
                 prompt_tokens=sum(len(e.tokens) for e in plan) - n_decode,
                 h2d_bytes=self.engine.last_h2d_bytes, d2h_bytes=4 * (len(tokens) + 1) if sampling else 0,
+                kv_tokens=kv_tokens, key_pairs=key_pairs,
             ))
             if len(self.step_log) > 100_000:
                 del self.step_log[:50_000]
