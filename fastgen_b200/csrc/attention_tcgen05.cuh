@@ -59,6 +59,26 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// ---- two float32 values in one 64-bit register: the packed arithmetic of sm_100 ----
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void f32x2_split(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 template <int HD>
 constexpr size_t smem_bytes() {
   // Q and two stages of K and V; plus alignment slack
@@ -383,28 +403,33 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
             for (int i = 0; i < KEYS / 2; ++i) packed[i] = 0u;
           } else {
             const float mc = m_ref * c;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint64_t c2 = f32x2(c, c), nmc2 = f32x2(-mc, -mc);
+            uint64_t sum2[2] = {f32x2(0.f, 0.f), f32x2(0.f, 0.f)};
 #pragma unroll
             for (int i = 0; i < KEYS; i += 4) {
-              const float p0 = ex2_approx(fmaf(s[i], c, -mc)), p1 = ex2_approx(fmaf(s[i + 1], c, -mc));
-              const float p2 = ex2_approx(fmaf(s[i + 2], c, -mc)), p3 = ex2_approx(fmaf(s[i + 3], c, -mc));
-              sum4[0] += p0;
-              sum4[1] += p1;
-              sum4[2] += p2;
-              sum4[3] += p3;
+              float x0, x1, x2, x3;
+              f32x2_split(fma_f32x2(f32x2(s[i], s[i + 1]), c2, nmc2), x0, x1);
+              f32x2_split(fma_f32x2(f32x2(s[i + 2], s[i + 3]), c2, nmc2), x2, x3);
+              const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+              sum2[0] = add_f32x2(sum2[0], f32x2(p0, p1));
+              sum2[1] = add_f32x2(sum2[1], f32x2(p2, p3));
               packed[i / 2] = pack_bf16(p0, p1);
               packed[i / 2 + 1] = pack_bf16(p2, p3);
             }
-            sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            float a0, a1, a2, a3;
+            f32x2_split(sum2[0], a0, a1);
+            f32x2_split(sum2[1], a2, a3);
+            sum = (a0 + a1) + (a2 + a3);
           }
           l_run = l_run * alpha + sum;
           // P_t over the first 32 columns of S_t (this thread has read all of its row)
           tmem_st32_raw(s_addr, packed);
-          // O_{t-1} is complete after this wait; O is then rescaled where a row's reference
-          // maximum was raised (warp-uniform decision).  (The barrier of this parity completes
-          // next for O_{t+1}, which needs this thread's P_{t+1}: the wait cannot fall behind.)
-          if (t > 0) mbar_wait(&o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1, status, &gave_up);
+          // Where a row's reference maximum was raised, O is rescaled before this tile's P V may
+          // run (warp-uniform decision), once O_{t-1} is complete; otherwise the warp does not
+          // wait for O at all.  (The barrier of this parity completes next for O_{t+1}, which
+          // needs this thread's P_{t+1}: a wait on it cannot fall behind.)
           if (t > 0 && __any_sync(0xffffffffu, raise)) {
+            mbar_wait(&o_done[(gt - 1) & 1], ((gt - 1) >> 1) & 1, status, &gave_up);
             tc_fence_after();
 #pragma unroll
             for (int cc = 0; cc < HD / 32; ++cc) {

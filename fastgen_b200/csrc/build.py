@@ -32,6 +32,8 @@ CSRC = Path(__file__).resolve().parent
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+# more flags for nvcc (say -DNAME=value for an experiment); they are part of a library's stamp
+EXTRA_FLAGS = os.environ.get("FASTGEN_B200_NVCC_FLAGS", "").split()
 
 CORE_SOURCES = [
     "errors.cu",
@@ -111,7 +113,7 @@ def _run(cmd: List[str], what: str) -> None:
 def _compile(name: str, sources: Sequence[str], defines: Iterable[str] = ()) -> Path:
     """Build ``lib<name>.so`` from ``sources`` unless an up-to-date one exists."""
     srcs = [CSRC / s for s in sources]
-    flags = ARCH_FLAGS + COMMON_FLAGS + [f"-D{d}" for d in defines]
+    flags = ARCH_FLAGS + COMMON_FLAGS + EXTRA_FLAGS + [f"-D{d}" for d in defines]
     digest = _digest(srcs, flags)
     # A library shipped beside the sources is used when it matches them, even
     # if this user cannot write there.
