@@ -31,6 +31,16 @@ LLAMA_8B = dict(
                       original_max_position_embeddings=8192, rope_type="llama3"),
     max_position_embeddings=131072,
 )
+# the layer sizes of Llama 3.2 1B / 3B (BASELINE.json configs 4 and 3), for --shape
+SHAPES = {
+    "8b": LLAMA_8B,
+    "3b": dict(LLAMA_8B, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28, num_attention_heads=24,
+               num_key_value_heads=8, tie_word_embeddings=True,
+               rope_scaling=dict(LLAMA_8B["rope_scaling"], factor=32.0)),
+    "1b": dict(LLAMA_8B, hidden_size=2048, intermediate_size=8192, num_hidden_layers=16, num_attention_heads=32,
+               num_key_value_heads=8, tie_word_embeddings=True,
+               rope_scaling=dict(LLAMA_8B["rope_scaling"], factor=32.0)),
+}
 PAGE = 64
 SEED = 4
 PREFILL_TOKENS = 2048
@@ -92,21 +102,22 @@ class ClockSampler:
                     samples=len(sm))
 
 
-def model_flops(cfg: dict, n_layers: int, t: int, rows: int) -> float:
-    """FLOPs of a whole-prompt step of t tokens with logits at `rows` places."""
+def model_flops(cfg: dict, n_layers: int, t: int, rows: int, cached: int = 0) -> float:
+    """FLOPs of a step of t prompt tokens on `cached` keys with logits at `rows` places."""
     d, f, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     hq, hkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     hd = d // hq
     per_layer = 2 * t * d * (hq + 2 * hkv) * hd + 2 * t * hq * hd * d + 3 * 2 * t * d * f
-    attn = 4 * hd * hq * t * (t + 1) / 2
+    attn = 4 * hd * hq * (t * cached + t * (t + 1) / 2)
     return n_layers * (per_layer + attn) + 2 * rows * d * v
 
 
 def describe_config(cfg: dict, batch: int, context: int, layers: int, layers_full: int, first: int, last: int,
-                    peaks_source: str) -> dict:
+                    peaks_source: str, shape: str = "8b") -> dict:
     """The sizes of the run, flat (the record keeps at most 20 keys of it, and no lists)."""
+    name = {"8b": "Llama-3.1-8B shape", "3b": "Llama-3.2-3B shape", "1b": "Llama-3.2-1B shape"}[shape]
     return {
-        "model": "Llama-3.1-8B shape", "global_batch": batch, "seq_len": context,
+        "model": name, "global_batch": batch, "seq_len": context,
         "parallelism": "single GPU", "layers": layers, "layers_full": layers_full,
         "hidden": cfg["hidden_size"], "ffn": cfg["intermediate_size"], "q_heads": cfg["num_attention_heads"],
         "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"],
@@ -125,7 +136,7 @@ def run_ours(args) -> dict:
     from fastgen_b200.sampling import Sampler
 
     pk = peaks()
-    cfg = dict(LLAMA_8B)
+    cfg = dict(SHAPES[args.shape])
     full_layers = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = args.layers or full_layers
     n_layers = cfg["num_hidden_layers"]
@@ -140,8 +151,13 @@ def run_ours(args) -> dict:
     prompt_len = max(1, (args.from_position if args.from_position else ctx_len - k) - w)
     max_b = max(args.batch, 64 if not args.skip_points else args.batch, 1)
     n_pages = max_b * (-(-(ctx_len + 1) // PAGE)) + PREFILL_TOKENS // PAGE + 2
+    longest = max(ctx_len, PREFILL_TOKENS)
+    if args.more_points:
+        # room for 8 requests of 65,536 tokens and for a portion of 8,192 on 32,768 cached keys
+        n_pages = max(n_pages, 8 * (65536 // PAGE + 1) + 8)
+        longest = max(longest, 65536)
     engine = Engine(model, page_size=PAGE, n_pages=n_pages, max_requests=max_b,
-                    max_length=max(ctx_len, PREFILL_TOKENS) + PAGE, num_cuda_graphs=max_b)
+                    max_length=longest + PAGE, num_cuda_graphs=max_b)
     sampler = Sampler(model.ops, vocab, max_b, use_sampling=False)
     gen = torch.Generator().manual_seed(SEED)
 
@@ -179,15 +195,16 @@ def run_ours(args) -> dict:
                    tflops=round(pre_flops / (pre_ms * 1e-3) / 1e12, 1), peak_tflops=pk["bf16_tflops"])
 
     # ---- decode, device-timed: K graph replays + sampling, tokens stay on the device ----
+    filled = []  # (profiling and the far points: the cache pages hold random values instead of real keys)
     weight_bytes = model.weight_bytes()  # every matrix once; the embedding table only if it is the output
     kv_per_token = model.cache_bytes_per_token(2)
 
-    def decode_run(batch, steps, warm, clocks=None):
+    def decode_run(batch, steps, warm, clocks=None, prompt_len=prompt_len, fast_fill=args.fast_fill):
         ids = [f"d{i}" for i in range(batch)]
         for rid in ids:
             engine.admit(rid)
         for rid in ids:  # fill the cache: the prompt in portions of 2,048
-            if args.fast_fill:
+            if fast_fill:
                 r = engine.cache.get(rid)
                 engine.cache.reserve(r, prompt_len)
                 engine.cache.advance(r, prompt_len)
@@ -195,10 +212,11 @@ def run_ours(args) -> dict:
             p = prompt(prompt_len)
             for s in range(0, prompt_len, PREFILL_TOKENS):
                 engine.step([StepEntry(rid, p[s:s + PREFILL_TOKENS], [])])
-        if args.fast_fill:
+        if fast_fill and not filled:
             for grp in engine.cache.groups:
                 grp.k_pages.normal_(0.0, 1.0)
                 grp.v_pages.normal_(0.0, 1.0)
+            filled.append(True)
         reqs = [engine.cache.get(rid) for rid in ids]
         slots = [r.slot for r in reqs]
         tokens = torch.randint(0, vocab, (batch,), generator=gen).to(dev, torch.int32)
@@ -291,15 +309,47 @@ def run_ours(args) -> dict:
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / pk["hbm_gbs"], 4)
     points[f"decode_b{args.batch}"] = round(main["tok_s"], 1)
+    if args.more_points:
+        # Further sizes: decode at contexts of 16,384 and 65,536 (the pages hold random values: a
+        # decode step's time does not depend on them), and prompt portions of 512 and 8,192 tokens
+        # on 8,192 and 32,768 cached keys.  Each with its fraction of the roofline.
+        for ctx in (16384, 65536):
+            for b in (1, 8):
+                r = decode_run(b, 64, w, prompt_len=ctx - 64 - w, fast_fill=True)
+                points[f"decode_b{b}_ctx{ctx // 1024}k"] = round(r["tok_s"], 1)
+                points[f"decode_b{b}_ctx{ctx // 1024}k_hbm_frac"] = round(r["gbs"] / pk["hbm_gbs"], 4)
+        for t, cached in ((512, 8192), (8192, 8192), (512, 32768), (8192, 32768), (8192, 0)):
+            portion = prompt(t)
+
+            def portion_once():
+                engine.admit("far")
+                r = engine.cache.get("far")
+                if cached:
+                    engine.cache.reserve(r, cached)
+                    engine.cache.advance(r, cached)
+                engine.step([StepEntry("far", portion, [t - 1])])
+                engine.release("far")
+
+            if not filled:
+                for grp in engine.cache.groups:
+                    grp.k_pages.normal_(0.0, 1.0)
+                    grp.v_pages.normal_(0.0, 1.0)
+                filled.append(True)
+            portion_once()
+            ms = min(event_ms(portion_once, 3))
+            flops = model_flops(cfg, n_layers, t, 1, cached)
+            key = f"prefill_t{t}_on{cached // 1024}k"
+            points[key] = round(t / ms * 1e3, 1)
+            points[key + "_tensor_frac"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
 
     return {
-        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (8B, bf16)",
+        "metric": f"decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens ({args.shape.upper()}, bf16)",
         "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": k, "warmup": w,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights seed 4, uniform random token ids)",
         "impl": "ours",
         "config": describe_config(cfg, args.batch, ctx_len, n_layers, full_layers, main["first"], main["last"],
-                                  pk["source"]),
+                                  pk["source"], args.shape),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(main["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(main["gbs"] / pk["hbm_gbs"], 4)},
@@ -316,7 +366,7 @@ def run_reference(args) -> dict:
         from reference_arm import run
     except Exception as e:  # the arm's own module is missing or broken
         return {"impl": "reference", "unavailable": f"reference arm not runnable: {e!r}"[:300]}
-    return run(args, LLAMA_8B)
+    return run(args, SHAPES[args.shape])
 
 
 def main() -> int:
@@ -332,7 +382,11 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="8b",
+                    help="layer sizes: Llama 3.1 8B (the benchmark's), Llama 3.2 3B or 1B")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--more-points", action="store_true",
+                    help="also measure decode at contexts of 16k and 64k and prompt portions on 8k and 32k cached keys")
     ap.add_argument("--skip-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the run through the Python entry point")
     ap.add_argument("--skip-decode", action="store_true", help="skip the decode measurement (profiling prefill)")

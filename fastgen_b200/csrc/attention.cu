@@ -169,7 +169,7 @@ extern "C" int fg_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         scale_log2, scratch, max_splits, status);
   FG_CHECK_LAUNCH("fg_attention_decode_bf16");
   dim3 cgrid(n_heads, n_seqs);
-  attention_combine_kernel<FG_HEAD_DIM><<<cgrid, 128, 0, stream>>>(
+  attention_combine_kernel<FG_HEAD_DIM><<<cgrid, COMBINE_THREADS, 0, stream>>>(
       scratch, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window, max_splits, nullptr, status);
   FG_CHECK_LAUNCH("fg_attention_combine");
   return 0;
@@ -251,7 +251,7 @@ extern "C" int fg_attention_decode_tma_bf16(const void* q, int q_stride, void* o
   }
   FG_CHECK_LAUNCH("fg_attention_decode_tma_bf16");
   dim3 cgrid(n_heads, n_seqs);
-  fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(128), 0, stream,
+  fg_launch_pdl(fg_mma::attention_combine_kernel<FG_HEAD_DIM>, cgrid, dim3(fg_mma::COMBINE_THREADS), 0, stream,
                 (const float*)partials, (__nv_bfloat16*)out, out_stride, pos, seq_req, seq_tok, n_heads, window,
                 max_splits, combine_pairs, status);
   FG_CHECK_LAUNCH("fg_attention_combine");

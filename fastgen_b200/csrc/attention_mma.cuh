@@ -555,9 +555,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 }
 
 // out[token, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m) over the
-// request's splits, in ascending split order.  One block per (head, token).
+// request's splits.  One block of COMBINE_THREADS per (head, token): warp w sums the splits
+// s_lo + w, s_lo + w + W, ... (a lane holds two neighbouring dimensions of every 64), then the
+// warps' sums are added in ascending warp order.  The order of the additions depends on the
+// request's own splits only, never on the batch.
+constexpr int COMBINE_THREADS = 256;
+
 template <int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(COMBINE_THREADS)
 attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, int out_stride,
                          const int* __restrict__ pos, const int* __restrict__ seq_req,
                          const int* __restrict__ seq_tok, int n_heads, int window, int max_splits,
@@ -565,9 +570,13 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   // first_pair (written by the kernel before, so no __restrict__): null, or for every
   // request the number of (request, split) pairs before it; the partials are then
   // numbered [pair][head] (only the splits that exist), else [request][head][split].
-  constexpr int CHUNK = 128;  // splits whose weights are staged at a time
-  __shared__ float w_s[CHUNK];
-  __shared__ float red[4];
+  constexpr int WARPS = COMBINE_THREADS / 32;
+  constexpr int NV = (HD + 63) / 64;  // float2 pieces a lane holds
+  constexpr int PS = part_stride<HD>();
+  static_assert(PS % 2 == 0, "partials are read as float2");
+  __shared__ float red[WARPS];
+  __shared__ float acc_s[WARPS][NV * 64];
+  __shared__ float ll_s[WARPS];
   pdl_trigger();
   pdl_wait();
   const int seq = blockIdx.y, head = blockIdx.x;
@@ -575,7 +584,7 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   const int tok = seq_tok[seq];
   __nv_bfloat16* dst = out + (size_t)tok * out_stride + head * HD;
   if (seq_req[seq] < 0) {
-    for (int d = tid; d < HD; d += blockDim.x) dst[d] = __float2bfloat16_rn(0.f);
+    for (int d = tid; d < HD; d += COMBINE_THREADS) dst[d] = __float2bfloat16_rn(0.f);
     return;
   }
   const int p = pos[tok];
@@ -586,7 +595,6 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
     if (tid == 0 && status) atomicOr(status, FG_STATUS_BAD_SPLITS);
     s_hi = max_splits - 1;
   }
-  constexpr int PS = part_stride<HD>();
   // base[s * step]: the partial of split s
   const size_t step = first_pair != nullptr ? (size_t)n_heads * PS : PS;
   const float* base = first_pair != nullptr
@@ -594,41 +602,50 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
                           : scratch + ((size_t)seq * n_heads + head) * max_splits * PS;
   // the overall maximum
   float mm = -INFINITY;
-  for (int s = s_lo + tid; s <= s_hi; s += blockDim.x) mm = fmaxf(mm, base[(size_t)s * step + HD]);
+  for (int s = s_lo + tid; s <= s_hi; s += COMBINE_THREADS) mm = fmaxf(mm, base[(size_t)s * step + HD]);
   mm = warp_max(mm);
   if (lane == 0) red[warp] = mm;
   __syncthreads();
-  mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  float acc[(HD + 127) / 128];
+  mm = red[0];
 #pragma unroll
-  for (int i = 0; i < (HD + 127) / 128; ++i) acc[i] = 0.f;
+  for (int w = 1; w < WARPS; ++w) mm = fmaxf(mm, red[w]);
+  // this warp's splits
+  float2 acc[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) acc[i] = make_float2(0.f, 0.f);
   float ll = 0.f;
-  for (int c0 = s_lo; c0 <= s_hi; c0 += CHUNK) {
-    const int n = min(CHUNK, s_hi - c0 + 1);
-    __syncthreads();
-    if (tid < n) {
-      const float ms = base[(size_t)(c0 + tid) * step + HD];
-      w_s[tid] = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-    }
-    __syncthreads();
-    // every thread accumulates the sum in the same ascending order
-    for (int s = 0; s < n; ++s) ll += w_s[s] * base[(size_t)(c0 + s) * step + HD + 1];
+#pragma unroll 4
+  for (int s = s_lo + warp; s <= s_hi; s += WARPS) {
+    const float* part = base + (size_t)s * step;
+    const float ms = part[HD];
+    const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+    ll += wgt * part[HD + 1];
 #pragma unroll
-    for (int i = 0; i < (HD + 127) / 128; ++i) {
-      const int d = tid + i * 128;
+    for (int i = 0; i < NV; ++i) {
+      const int d = i * 64 + lane * 2;
       if (d < HD) {
-        float a = acc[i];
-#pragma unroll 8
-        for (int s = 0; s < n; ++s) a += w_s[s] * base[(size_t)(c0 + s) * step + d];
-        acc[i] = a;
+        const float2 v = *reinterpret_cast<const float2*>(part + d);
+        acc[i].x += wgt * v.x;
+        acc[i].y += wgt * v.y;
       }
     }
   }
-  const float inv = ll > 0.f ? 1.f / ll : 0.f;
 #pragma unroll
-  for (int i = 0; i < (HD + 127) / 128; ++i) {
-    const int d = tid + i * 128;
-    if (d < HD) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+  for (int i = 0; i < NV; ++i) {
+    acc_s[warp][i * 64 + lane * 2] = acc[i].x;
+    acc_s[warp][i * 64 + lane * 2 + 1] = acc[i].y;
+  }
+  if (lane == 0) ll_s[warp] = ll;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) total += ll_s[w];
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  for (int d = tid; d < HD; d += COMBINE_THREADS) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) a += acc_s[w][d];
+    dst[d] = __float2bfloat16_rn(a * inv);
   }
 }
 
