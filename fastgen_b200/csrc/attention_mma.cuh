@@ -583,10 +583,9 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok = seq_tok[seq];
   __nv_bfloat16* dst = out + (size_t)tok * out_stride + head * HD;
-  if (seq_req[seq] < 0) {
-    for (int d = tid; d < HD; d += COMBINE_THREADS) dst[d] = __float2bfloat16_rn(0.f);
-    return;
-  }
+  // a padding lane has no request: nothing is written for it (its token index may be any row,
+  // also one that belongs to a request of the step)
+  if (seq_req[seq] < 0) return;
   const int p = pos[tok];
   const int s_lo = window > 0 ? max(0, p - window + 1) / DECODE_SPLIT : 0;
   int s_hi = p / DECODE_SPLIT;  // inclusive

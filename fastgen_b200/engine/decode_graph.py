@@ -154,6 +154,11 @@ class DecodeGraphs:
             # function attributes get set), then capture
             model.forward(ctx, memories)
             self.warmed.add(size)
+        b.graph, b.logits, b.n_kernels = self.capture(lambda: model.forward(ctx, memories))
+
+    def capture(self, forward):
+        """Capture ``forward()`` into a new graph of the shared memory pool.  Returns the graph,
+        what ``forward`` returned and the number of this package's kernels in it."""
         graph = torch.cuda.CUDAGraph()
         before = Ops.launches
         # Captured by hand on a stream of its own: torch.cuda.graph() would also run the
@@ -171,14 +176,13 @@ class DecodeGraphs:
                 kw = {} if self.pool is None else {"pool": self.pool}
                 graph.capture_begin(**kw)
                 try:
-                    b.logits = model.forward(ctx, memories)
+                    result = forward()
                 finally:
                     graph.capture_end()
             torch.cuda.current_stream().wait_stream(self.capture_stream)
         finally:
             if gc_was_on:
                 gc.enable()
-        b.n_kernels = Ops.launches - before
         if self.pool is None:
             self.pool = graph.pool()
-        b.graph = graph
+        return graph, result, Ops.launches - before

@@ -163,7 +163,8 @@ class Fastgen:
 
         self.engine = Engine(
             model, page_size=block, n_pages=max_seq // block, max_requests=self.max_batch,
-            max_length=min(model.args.max_positions, max_seq),
+            max_length=min(model.args.max_positions, max_seq), num_cuda_graphs=args.num_cuda_graphs,
+            max_step_tokens=self.max_prefill,
         )
         logger.info("Cache bytes per token: %d", per_token)
         logger.info("Allocated kv cache: %d pages of %d tokens", max_seq // block, block)

@@ -116,8 +116,11 @@ class StepContext:
             tiles = self._tiles[key] = self._build_tiles(tokens_per_tile, min_tokens)
         return tiles
 
-    def _build_tiles(self, tpt: int, min_tokens: int) -> AttentionTiles:
-        tiles = []  # (keys the tile reads, slot, first token, tokens)
+    def host_tiles(self, tpt: int, min_tokens: int) -> List[Tuple[int, int, int, int]]:
+        """The tiles as host tuples (keys the tile reads, slot, first token, tokens), ascending
+        by the keys: the kernels hand out the list from its end, so the tiles with the most keys
+        start first and the short ones fill the tail of the launch."""
+        tiles = []
         for b, slot in enumerate(self.host_seq_slot):
             start, end = self.host_seq_start[b], self.host_seq_start[b + 1]
             if end - start < min_tokens:
@@ -126,9 +129,11 @@ class StepContext:
             for t in range(start, end, tpt):
                 n_tok = min(tpt, end - t)
                 tiles.append((cached + t - start + n_tok, slot, t, n_tok))
-        # ascending by work: the kernels hand out the list from its end, so the tiles with
-        # the most keys start first and the short ones fill the tail of the launch
         tiles.sort(key=lambda tile: tile[0])
+        return tiles
+
+    def _build_tiles(self, tpt: int, min_tokens: int) -> AttentionTiles:
+        tiles = self.host_tiles(tpt, min_tokens)
         req = [tile[1] for tile in tiles]
         tok0 = [tile[2] for tile in tiles]
         ntok = [tile[3] for tile in tiles]
@@ -169,7 +174,12 @@ class Engine:
         max_length: Optional[int] = None,
         num_cuda_graphs: int = 16,
         use_graphs: Optional[bool] = None,
+        max_step_tokens: Optional[int] = None,
     ) -> None:
+        """``max_step_tokens``: steps of up to that many tokens that are not single tokens only
+        (prompt portions, alone or beside decoded tokens) replay CUDA graphs too, captured per
+        padded shape when first met (``engine/step_graph.py``); ``None``: such steps are launched
+        kernel by kernel."""
         self.model = model
         self.ops = model.ops
         self.device = model.ops.device
@@ -197,6 +207,11 @@ class Engine:
         use_graphs = use_graphs and all(b.mixer.graph_safe for b in model.blocks)
         # steps of single tokens replay a captured graph (as generate.py:296-347)
         self.graphs = _decode_graphs()(self, max_requests, num_cuda_graphs) if use_graphs else None
+        self.step_graphs = None
+        if self.graphs is not None and max_step_tokens:
+            from .step_graph import StepGraphs
+
+            self.step_graphs = StepGraphs(self, self.graphs, max_step_tokens)
 
     # -- requests --------------------------------------------------------------
     def admit(self, request_id) -> RequestCache:
@@ -239,7 +254,9 @@ class Engine:
             reqs.append(req)
         return reqs
 
-    def build_context(self, entries: Sequence[StepEntry], reqs: Sequence[RequestCache]) -> StepContext:
+    def host_context(self, entries: Sequence[StepEntry], reqs: Sequence[RequestCache]):
+        """The step on the host: a context with the sequences' lists, and per token its id,
+        position and slot, and the wanted rows."""
         ctx = StepContext(self.device)
         tokens, pos, rq, want = [], [], [], []
         for e, req in zip(entries, reqs):
@@ -252,6 +269,10 @@ class Engine:
             ctx.host_seq_slot.append(req.slot)
             ctx.host_seq_cached.append(req.length)
             ctx.host_seq_start.append(base + n)
+        return ctx, tokens, pos, rq, want
+
+    def build_context(self, entries: Sequence[StepEntry], reqs: Sequence[RequestCache], host=None) -> StepContext:
+        ctx, tokens, pos, rq, want = host if host is not None else self.host_context(entries, reqs)
         t, b, nw = len(tokens), len(entries), len(want)
         packed = np.concatenate(
             [
@@ -317,5 +338,15 @@ class Engine:
             )
             self.last_h2d_bytes = self.graphs.last_h2d_bytes
             return logits
-        ctx = self.build_context(entries, reqs)
+        host = self.host_context(entries, reqs)
+        if self.step_graphs is not None:
+            ctx, tokens, pos, rq, want = host
+            n_singles = sum(1 for e in entries if len(e.tokens) == 1)
+            key = self.step_graphs.shape_for(len(tokens), len(want), n_singles, len(entries))
+            # a padded shape that is not much larger than the step: the padding is computed too
+            if key is not None and key[0] - len(tokens) <= max(64, len(tokens) // 8):
+                logits = self.step_graphs.run(key, ctx, tokens, pos, rq, want)
+                self.last_h2d_bytes = self.step_graphs.last_h2d_bytes
+                return logits
+        ctx = self.build_context(entries, reqs, host)
         return self.model.forward(ctx, self.memories)

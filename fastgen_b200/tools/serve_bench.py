@@ -131,6 +131,7 @@ def main() -> int:
     ap.add_argument("--max-prefill", type=int, default=0, help="tokens a step (0: the workload's own)")
     ap.add_argument("--sync-freq", type=int, default=10)
     ap.add_argument("--page", type=int, default=64)
+    ap.add_argument("--graphs", type=int, default=32, help="most decode graphs (batch buckets)")
     ap.add_argument("--arrive-over", type=float, default=None,
                     help="seconds over which the requests arrive (0: all at once; default: the workload's own)")
     args = ap.parse_args()
@@ -150,7 +151,7 @@ def main() -> int:
     longest = sorted((len(p) + g for p, g in reqs), reverse=True)[:max_batch]
     max_seq = sum(-(-(n + 1) // args.page) * args.page for n in longest) + 2 * args.page
     gen_args = GenArgs(use_sampling=False, max_batch=max_batch, max_seq=max_seq, cache_block=args.page,
-                       max_prefill=args.max_prefill or w["max_prefill"], num_cuda_graphs=max_batch,
+                       max_prefill=args.max_prefill or w["max_prefill"], num_cuda_graphs=min(max_batch, args.graphs),
                        sync_freq=args.sync_freq)
     fg = Fastgen(gen_args, model, stop_tokens=[])
 

@@ -214,7 +214,7 @@ def plan_many(requests: Dict[str, List[int]], seed: int, max_live: int = 14, adm
 
 
 def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_requests: int = 4,
-               num_cuda_graphs: int = 16, before_step=None):
+               num_cuda_graphs: int = 16, before_step=None, max_step_tokens=None):
     """Replay ``steps`` through the package's engine in this process.  ``before_step(engine,
     step)`` runs before each step, after the requests it brings have been admitted."""
     from fastgen_b200.engine import Engine, Model, StepEntry
@@ -223,7 +223,7 @@ def run_engine(model_dir, dtype, steps, page_size: int, max_tokens: int, max_req
     n_pages = max(1, -(-max_tokens // page_size))
     engine = Engine(model, page_size=page_size, n_pages=n_pages, max_requests=max_requests,
                     max_length=min(model.args.max_positions, n_pages * page_size),
-                    num_cuda_graphs=num_cuda_graphs)
+                    num_cuda_graphs=num_cuda_graphs, max_step_tokens=max_step_tokens)
     outputs, live = {}, set()
     for st in steps:
         entries = []

@@ -52,6 +52,37 @@ def test_replay(tmp_path, name, dtype, plan):
     assert all(f == g.pool.n_pages for f, g in zip(engine.cache.free_pages(), engine.cache.groups))
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_c", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("plan", ["portions", "mixed", "many"])
+def test_replay_with_graphs_for_prompt_steps(tmp_path, name, dtype, plan):
+    """The same replays with every step of up to 512 tokens replayed from a CUDA graph of its
+    padded shape (tokens of slot -1 behind the step's own, tile lists padded with tiles of no
+    request): prompt portions down to two tokens, portions beside decoded tokens, many
+    requests.  What the generator does for steps up to its token budget."""
+    model_dir = H.make_model_dir(tmp_path, name)
+    page = PAGES[name]
+    if plan == "portions":
+        reqs = _requests(name, LENGTHS[name], 100)
+        steps = H.plan_portions(reqs)
+        kw = dict(max_requests=4)
+    elif plan == "mixed":
+        reqs = _requests(name, LENGTHS[name] + [48, 17, 80], 200)
+        steps = H.plan_mixed(reqs, seed=5)
+        kw = dict(max_requests=4)
+    else:
+        reqs = _requests(name, MANY.get(name, MANY["tiny_b"])[:12], 500)
+        reqs = {k: v[: H.CONFIGS[name][0]["max_position_embeddings"] - 8] for k, v in reqs.items()}
+        steps = H.plan_many(reqs, seed=9, max_live=10)
+        kw = dict(max_requests=10, num_cuda_graphs=3)
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page, H.max_live_tokens(steps, page) + 2 * page,
+                                   max_step_tokens=512, **kw)
+    assert engine.step_graphs is not None and engine.step_graphs.replays >= 4
+    got = H.collect(steps, outputs)
+    H.compare(model_dir, reqs, got, dtype)
+    assert engine.cache.n_live == 0
+
+
 MANY = {"tiny_b": [30, 120, 75, 260, 41, 33, 180, 90, 64, 129, 200, 57, 310, 48, 150, 99],
         "tiny_d": [70, 300, 131, 420, 45, 260, 129, 64, 390, 200, 88, 333, 150, 257, 40, 512],
         "tiny_e": [50, 150, 260, 64, 129, 400, 33, 300, 210, 101, 99, 380, 45, 128, 256, 170]}
