@@ -27,6 +27,7 @@ from ..csrc.ops import Ops
 from .step import AttentionTiles, SingleTokens, StepContext
 
 _RING = 4
+MAX_SHAPES = 24  # captured shapes kept; the least recently used one goes when another is needed
 
 
 def token_buckets(max_tokens: int) -> List[int]:
@@ -140,9 +141,15 @@ class StepGraphs:
             req: Sequence[int], want: Sequence[int]) -> Optional[torch.Tensor]:
         """Replay the graph of shape ``key`` for the step described by the host lists (and by
         ``ctx_host``'s sequences).  Returns logits ``[len(want), vocab]``."""
-        sh = self.shapes.get(key)
+        sh = self.shapes.pop(key, None)
         if sh is None:
-            sh = self.shapes[key] = _Shape(*key, self.max_seqs, self.max_len, self.keys_bound, self.device)
+            while len(self.shapes) >= MAX_SHAPES:
+                # every shape holds its graph's memory and a [rows, vocabulary] logits buffer
+                old = self.shapes.pop(next(iter(self.shapes)))
+                torch.cuda.current_stream().synchronize()  # its last replay is over
+                old.graph = old.logits = None
+            sh = _Shape(*key, self.max_seqs, self.max_len, self.keys_bound, self.device)
+        self.shapes[key] = sh  # (most recently used last)
         if sh.graph is None:
             self._capture(sh)
         slot = sh.ring_next
