@@ -234,7 +234,7 @@ def test_fgchat_token_id_mode(tmp_path):
 
 def test_fgchat_token_id_mode_keeps_the_conversation(tmp_path):
     """The second round's prompt is the first prompt, the first answer and the new line; ``/r 2``
-    goes back to the state before round 2."""
+    goes back to the state before the second exchange."""
     import re
     model_dir = H.make_model_dir(tmp_path, "tiny_b", std=0.08)  # weights under which the history matters
     root = Path(__file__).resolve().parent.parent

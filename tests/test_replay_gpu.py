@@ -149,6 +149,32 @@ def test_a_wrong_page_breaks_the_comparison(tmp_path, name, dtype):
         H.record_ratios = True
 
 
+# hidden, feed-forward, vocabulary, query heads, key/value heads, head size: widths that are odd, no
+# multiple of 4 or of 8, a vocabulary of 7, groups of 5 heads, and head sizes between and beyond
+# those of the tiny configurations (each has its own attention library)
+ODD_SIZES = [(257, 129, 1001, 5, 1, 64), (90, 66, 97, 4, 2, 32), (100, 70, 101, 2, 1, 16), (36, 20, 7, 1, 1, 128),
+             (136, 200, 211, 3, 1, 80), (136, 200, 211, 3, 1, 160), (136, 200, 211, 3, 1, 256)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("sizes", ODD_SIZES, ids=lambda s: "x".join(map(str, s)))
+def test_replay_at_odd_sizes(tmp_path, sizes, dtype):
+    """Kernels take every size a configuration allows, or refuse it with an error: never a wrong
+    result.  Mixed replay with reused pages, as above."""
+    from fastgen_b200.weights import write_random_model
+
+    hidden, ffn, vocab, hq, hkv, hd = sizes
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=hidden, intermediate_size=ffn, num_hidden_layers=2,
+               num_attention_heads=hq, num_key_value_heads=hkv, head_dim=hd, rms_norm_eps=1e-5, vocab_size=vocab,
+               tie_word_embeddings=bool(hidden % 4), rope_theta=10000.0, max_position_embeddings=300)
+    model_dir = write_random_model(tmp_path / "odd", cfg, seed=hidden + hd, norm_jitter=0.1)
+    reqs = {f"r{i}": H.random_tokens(vocab, n, hidden + i) for i, n in enumerate([5, 150, 260, 64, 33])}
+    steps = H.plan_mixed(reqs, seed=3)
+    outputs, engine = H.run_engine(model_dir, dtype, steps, 8, H.max_live_tokens(steps, 8))
+    H.compare(model_dir, reqs, H.collect(steps, outputs), dtype)
+    assert engine.cache.n_live == 0
+
+
 @pytest.mark.parametrize("dtype,name,page", [("float32", "tiny_b", None), ("bfloat16", "tiny_b", None),
                                              ("bfloat16", "tiny_d", 256), ("float32", "tiny_d", 48)])
 def test_trace_run_program(tmp_path, dtype, name, page):
