@@ -578,15 +578,18 @@ attention_combine_kernel(const float* scratch, __nv_bfloat16* __restrict__ out, 
   __shared__ float acc_s[WARPS][NV * 64];
   __shared__ float ll_s[WARPS];
   pdl_trigger();
-  pdl_wait();
+  // the lists of sequences and positions are inputs of the step: read while the kernel before
+  // this one finishes; its partials (and first_pair) are touched after the wait
   const int seq = blockIdx.y, head = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok = seq_tok[seq];
+  const int request = seq_req[seq];
+  const int p = request < 0 ? 0 : pos[tok];
+  pdl_wait();
   __nv_bfloat16* dst = out + (size_t)tok * out_stride + head * HD;
   // a padding lane has no request: nothing is written for it (its token index may be any row,
   // also one that belongs to a request of the step)
-  if (seq_req[seq] < 0) return;
-  const int p = pos[tok];
+  if (request < 0) return;
   const int s_lo = window > 0 ? max(0, p - window + 1) / DECODE_SPLIT : 0;
   int s_hi = p / DECODE_SPLIT;  // inclusive
   if (s_hi >= max_splits) {

@@ -84,10 +84,18 @@ rmsnorm_vec_kernel(TH* h, const TD* delta, const void* __restrict__ w, int w_dty
   // loads stay below the wait
   __shared__ float scratch[32];
   pdl_trigger();
-  pdl_wait();
+  // the norm's weight and the row indices do not depend on the kernels before this one: they are
+  // on their way while those finish, instead of being a second round trip behind the reduction
+  float4 ww[ITEMS];
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int d = (it * VEC_THREADS + threadIdx.x) * 4;
+    ww[it] = (out != nullptr && d < dim) ? load4_any(w, w_dtype, d) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const size_t base = (size_t)(rows ? rows[blockIdx.x] : blockIdx.x) * dim;
   const size_t obase = (size_t)blockIdx.x * dim;
   const bool store_h = delta != nullptr && rows == nullptr;
+  pdl_wait();
   float4 v[ITEMS];
   float ss = 0.f;
 #pragma unroll
@@ -113,11 +121,9 @@ rmsnorm_vec_kernel(TH* h, const TD* delta, const void* __restrict__ w, int w_dty
 #pragma unroll
   for (int it = 0; it < ITEMS; ++it) {
     const int d = (it * VEC_THREADS + threadIdx.x) * 4;
-    if (d < dim) {
-      const float4 ww = load4_any(w, w_dtype, d);
-      store4<TO>(out + obase + d, make_float4(v[it].x * rstd * ww.x, v[it].y * rstd * ww.y,
-                                              v[it].z * rstd * ww.z, v[it].w * rstd * ww.w));
-    }
+    if (d < dim)
+      store4<TO>(out + obase + d, make_float4(v[it].x * rstd * ww[it].x, v[it].y * rstd * ww[it].y,
+                                              v[it].z * rstd * ww[it].z, v[it].w * rstd * ww[it].w));
   }
 }
 
