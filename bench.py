@@ -44,6 +44,7 @@ SHAPES = {
 PAGE = 64
 SEED = 4
 PREFILL_TOKENS = 2048
+SETTLE_S = 0.5  # pause between filling the cache and the decode steps
 
 
 def peaks() -> dict:
@@ -122,7 +123,7 @@ def describe_config(cfg: dict, batch: int, context: int, layers: int, layers_ful
         "hidden": cfg["hidden_size"], "ffn": cfg["intermediate_size"], "q_heads": cfg["num_attention_heads"],
         "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"],
         "vocab": cfg["vocab_size"], "page": PAGE, "decode_from": first, "decode_to": last,
-        "prefill_tokens": PREFILL_TOKENS,
+        "prefill_tokens": PREFILL_TOKENS, "settle_s": SETTLE_S,
         "l2": "inputs larger than L2 (all weights are streamed every step)", "peaks": peaks_source,
     }
 
@@ -157,7 +158,9 @@ def run_ours(args) -> dict:
         n_pages = max(n_pages, 8 * (65536 // PAGE + 1) + 8)
         longest = max(longest, 65536)
     engine = Engine(model, page_size=PAGE, n_pages=n_pages, max_requests=max_b,
-                    max_length=longest + PAGE, num_cuda_graphs=max_b)
+                    max_length=longest + PAGE, num_cuda_graphs=max_b,
+                    # prompt steps replay CUDA graphs of their padded shape, as in the generator
+                    max_step_tokens=8192 if args.more_points else PREFILL_TOKENS)
     sampler = Sampler(model.ops, vocab, max_b, use_sampling=False)
     gen = torch.Generator().manual_seed(SEED)
 
@@ -232,6 +235,10 @@ def run_ours(args) -> dict:
             for r in reqs:
                 engine.cache.advance(r, r.length + 1)
 
+        # the prompts' prefill has just run at the power cap: let the clocks settle before the
+        # decode steps are warmed up and timed (nothing runs meanwhile)
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)
         for _ in range(warm):
             one_step()
         torch.cuda.synchronize()
