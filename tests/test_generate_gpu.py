@@ -351,3 +351,48 @@ def test_default_gen_args_pad_their_graphs(tmp_path):
     for i, p in enumerate(prompts):
         assert out[i] == pl.greedy(model, p, 10)
     fg.destroy()
+
+
+def test_fgchat_text_mode_with_a_tokenizer(tmp_path):
+    """A model folder with tokenizer files: the dialog goes through the chat template, the answer
+    comes back as text, and the stop token (the tokenizer's eos) ends it."""
+    import json
+    import re
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import WhitespaceSplit
+
+    model_dir = H.make_model_dir(tmp_path, "tiny_a")
+    words = ["<s>", "</s>", "<unk>", "user", "assistant", ":", "hello", "world", "how", "are", "you"] + \
+            [f"w{i}" for i in range(11, 256)]
+    tk = Tokenizer(WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tk.pre_tokenizer = WhitespaceSplit()
+    tk.save(str(model_dir / "tokenizer.json"))
+    template = ("{{ bos_token }} {% for m in messages %}{{ m['role'] }} : {{ m['content'] }} {% endfor %}"
+                "{% if add_generation_prompt %}assistant :{% endif %}")
+    (model_dir / "tokenizer_config.json").write_text(
+        json.dumps(dict(bos_token="<s>", eos_token="</s>", chat_template=template)))
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run(
+        [sys.executable, str(root / "bin" / "fgchat"), str(model_dir), "--temperature", "0.0",
+         "--max-tokens", "6", "--dtype", "fp32", "--page-size", "8", "--max-seq", "128"],
+        input="hello world\nhow are you\n/q\n", text=True, capture_output=True, timeout=600,
+    )
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    model = pl.read_model(model_dir)
+    ids = lambda text: [words.index(w) for w in text.split()]
+    first_prompt = ids("<s> user : hello world assistant :")
+    first = pl.greedy(model, first_prompt, 6)
+    if 1 in first:  # the eos token ends an answer and is not shown
+        first = first[: first.index(1) + 1]
+    shown = [t for t in first if t != 1] if first and first[-1] == 1 else first
+    lines = [re.sub(r"^(\d+> )+", "", l) for l in proc.stdout.splitlines()]
+    assert " ".join(words[t] for t in shown) in lines, proc.stdout
+    assert f"--- [{len(first)} tokens," in proc.stdout
+    second_prompt = ids("<s> user : hello world assistant : " + " ".join(words[t] for t in shown) +
+                        " user : how are you assistant :")
+    second = pl.greedy(model, second_prompt, 6)
+    if 1 in second:
+        second = second[: second.index(1) + 1]
+    shown2 = [t for t in second if t != 1] if second and second[-1] == 1 else second
+    assert " ".join(words[t] for t in shown2) in lines, proc.stdout
