@@ -318,13 +318,43 @@ extern "C" int fg_attention_prefill_tc5_supported() { return 1; }
 // fg_attention_prefill_tma_bf16, plus `work_counter`: one unsigned int on the device that is
 // zero between launches (the kernel leaves it so) and is not shared by launches that can
 // run at the same time; the tensor maps must have boxes of min(page, 64) rows.
+//
+// A launch of fewer items than resident blocks works on its long items in several parts (see
+// the kernel).  That needs, for every (item, part), fg_tc5::ROWS * (head size + 2) floats of
+// `split_scratch`, and an int of `split_flags` for every item (the kernel writes there in how
+// many parts it worked on the item; a second kernel adds the parts up).
+// fg_attention_prefill_tc5_split_slots says how many (item, part) pairs a launch wants room
+// for, or 0 if it would not split: too many items, or, where the host knows the most keys an
+// item reads (`max_keys`, else -1), too few keys for a second part.  With null pointers or
+// less room (`split_slots`) the launch does not split either.
+static long long tc5_items(int n_tiles, int n_heads, int n_kv_heads) {
+  const int group = n_heads / n_kv_heads;
+  const int hpb = group < fg_tc5::ROWS ? group : fg_tc5::ROWS;
+  return (long long)n_tiles * n_kv_heads * ((group + hpb - 1) / hpb);
+}
+
+static int tc5_parts(long long items) {
+  const long long parts = 2ll * sm_count() / (items > 0 ? items : 1);
+  return (int)(parts < 1 ? 1 : parts > fg_tc5::MAX_PARTS ? fg_tc5::MAX_PARTS : parts);
+}
+
+extern "C" int fg_attention_prefill_tc5_split_slots(int n_tiles, int n_heads, int n_kv_heads, int max_keys) {
+  if (n_tiles <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return 0;
+  // an item is split from 2 * SPLIT_MIN_TILES key tiles on
+  if (max_keys >= 0 && max_keys <= (2 * fg_tc5::SPLIT_MIN_TILES - 1) * fg_tc5::KEYS) return 0;
+  const long long items = tc5_items(n_tiles, n_heads, n_kv_heads);
+  const int parts = tc5_parts(items);
+  return parts > 1 ? (int)(items * parts) : 0;
+}
+
 extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* out, int out_stride,
                                              const void* k_map, const void* v_map, int layer,
                                              const int* block_table, int table_width, int page_size,
                                              int n_pages, const int* pos, const int* tile_req,
                                              const int* tile_tok0, const int* tile_ntok, int n_tiles,
                                              int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                             unsigned int* work_counter, int* status, cudaStream_t stream) {
+                                             unsigned int* work_counter, float* split_scratch, int* split_flags,
+                                             int split_slots, int max_keys, int* status, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(work_counter != nullptr, "fg_attention_prefill_tc5_bf16: no work counter");
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tc5_bf16: library built for head size %d, got %d",
@@ -341,30 +371,44 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
   memcpy(&km, k_map, sizeof(CUtensorMap));
   memcpy(&vm, v_map, sizeof(CUtensorMap));
   constexpr size_t smem = fg_tc5::smem_bytes<FG_HEAD_DIM>();
-  auto kern = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM>;
+  auto kern_whole = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, false>;
+  auto kern_parts = fg_tc5::attention_prefill_tc5_kernel<FG_HEAD_DIM, true>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kern_whole, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kern_parts, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FG_CHECK_ARG(e == cudaSuccess, "fg_attention_prefill_tc5_bf16: shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
   // two blocks an SM take the (tile, kv head, slice of the group) items from a counter
-  const long long total = (long long)n_tiles * n_kv_heads * ((group + hpb - 1) / hpb);
-  FG_CHECK_ARG(total < (1ll << 31), "fg_attention_prefill_tc5_bf16: %lld work items in one call", total);
+  const long long items = tc5_items(n_tiles, n_heads, n_kv_heads);
+  FG_CHECK_ARG(items < (1ll << 30), "fg_attention_prefill_tc5_bf16: %lld work items in one call", items);
+  const int want = fg_attention_prefill_tc5_split_slots(n_tiles, n_heads, n_kv_heads, max_keys);
+  const int parts = (want > 0 && split_scratch && split_flags && want <= split_slots) ? tc5_parts(items) : 1;
+  const long long total = items * parts;
   const long long resident = 2ll * sm_count();
   const int grid = (int)(total < resident ? total : resident);
-  kern<<<grid, fg_tc5::THREADS, smem, stream>>>(km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
-                                        out_stride, block_table, table_width, page_size, n_pages, pos, tile_req,
-                                        tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
-                                        scale * 1.4426950408889634f, work_counter, status);
+  (parts > 1 ? kern_parts : kern_whole)<<<grid, fg_tc5::THREADS, smem, stream>>>(
+      km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
+      page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
+      scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, status);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
+  if (parts > 1) {
+    dim3 mgrid(fg_tc5::ROWS * (FG_HEAD_DIM / 8) / fg_tc5::MERGE_THREADS, (unsigned int)items);
+    fg_launch_pdl(fg_tc5::attention_prefill_merge_kernel<FG_HEAD_DIM>, mgrid, dim3(fg_tc5::MERGE_THREADS), 0, stream,
+                  (const float*)split_scratch, (const int*)split_flags, parts, (__nv_bfloat16*)out, out_stride,
+                  tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb);
+    FG_CHECK_LAUNCH("fg_attention_prefill_merge");
+  }
   return 0;
 }
 #else
 extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
+extern "C" int fg_attention_prefill_tc5_split_slots(int, int, int, int) { return 0; }
 #endif
 #else
 extern "C" int fg_attention_decode_tma_supported() { return 0; }
 extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
+extern "C" int fg_attention_prefill_tc5_split_slots(int, int, int, int) { return 0; }
 extern "C" int fg_attention_decode_is_persistent(int, int, int, int) { return 0; }
 #endif

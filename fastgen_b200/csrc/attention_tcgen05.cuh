@@ -43,6 +43,8 @@ constexpr int LOAD_WARP = 4, MMA_WARP = 5;
 constexpr int KV_HALF = KEYS * 128;   // bytes of one 64-element half of a K or V tile
 constexpr int Q_HALF = ROWS * 128;    // ... of the Q tile
 constexpr float RESCALE_THRESHOLD = 8.f;  // in units of log2
+constexpr int SPLIT_MIN_TILES = 8;        // fewest key tiles of a part of a split item
+constexpr int MAX_PARTS = 32;             // most parts of an item
 
 // 2^x as the special-function unit gives it (relative error about 2^-22, results below
 // 2^-126 flushed to zero): the probabilities are rounded to bfloat16 right after, and
@@ -86,7 +88,27 @@ constexpr size_t smem_bytes() {
 }
 constexpr int TMEM_COLS = 256;  // S0, S1 (64 columns each; P overwrites its S) + O (HD <= 128)
 
+// The partial of one part of a split item: this thread's row of O (tensor memory, unnormalised),
+// its reference maximum (in units of log2) and its row sum, to [column][row] in `slot` (which
+// already points at the row), so that a warp's rows are neighbours.  Not inlined: the kernel's
+// main loop is sensitive to what the compiler makes of the code around it.
 template <int HD>
+__device__ __noinline__ void write_partial(uint32_t o_addr, float* slot, float m, float l) {
+#pragma unroll
+  for (int cc = 0; cc < HD / 32; ++cc) {
+    float o[32];
+    tmem_ld32(o_addr + cc * 32, o);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) __stcg(slot + (size_t)(cc * 32 + i) * ROWS, o[i]);
+  }
+  __stcg(slot + (size_t)HD * ROWS, m);
+  __stcg(slot + (size_t)(HD + 1) * ROWS, l);
+}
+
+// SPLIT: the instantiation for launches that work on long items in parts (`parts` > 1); the
+// other one has none of that code (its main loop proved sensitive to it: head size 64 ran 5 %
+// slower with it).
+template <int HD, bool SPLIT>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              int layer, const __nv_bfloat16* __restrict__ q, int q_stride,
@@ -95,7 +117,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
                              const int* __restrict__ tile_ntok, int n_tiles_total, int n_kv_heads, int group,
                              int heads_per_block, int window, float scale_log2, unsigned int* work_counter,
-                             int* status) {
+                             int parts, float* split_scratch, int* split_flags, int* status) {
   static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
   constexpr int HALVES = HD / 64;
   constexpr int STAGE_BYTES = HALVES * KV_HALF;
@@ -114,9 +136,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // drained: used once, at the end of a block one of whose waits ran out.
   __shared__ __align__(8) uint64_t full_k[2], full_v[2], s_done[2], p_ready[2], o_done[2], drained;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int first_pos_s;
   __shared__ unsigned int work_s;
   __shared__ int gave_up;  // set by a wait that ran out: the waits after it return at once (see mbar_wait)
+  __shared__ int first_pos_s;
   constexpr int PAGE_STAGE = 256;
   __shared__ int box_pages[PAGE_STAGE];
 
@@ -158,19 +180,31 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // launch had ended would wait for its SM to drain.  The list is in ascending order of
   // work and is handed out from its end with the heads running fastest, so the longest
   // items start first and the short ones fill the tail.
+  //
+  // A launch of fewer items than resident blocks would leave SMs idle and be bound by its
+  // longest item.  With `parts` > 1 every item is `parts` draws that follow each other in the
+  // hand-out: an item of many key tiles is worked on in up to `parts` stretches of at least
+  // SPLIT_MIN_TILES tiles (the draws beyond that do nothing).  Every part of such an item
+  // leaves its unnormalised O, its reference maximum and its row sums in `split_scratch`, and
+  // `split_flags[item]` says how many parts there are (0: the item wrote its output itself);
+  // attention_prefill_merge_kernel, launched behind this one, adds the partials up.
   const unsigned int n_subs = (group + heads_per_block - 1) / heads_per_block;
-  const unsigned int total_work = (unsigned int)n_tiles_total * n_kv_heads * n_subs;
+  if (!SPLIT) parts = 1;
+  const unsigned int total_work = (unsigned int)n_tiles_total * n_kv_heads * n_subs * parts;
   const unsigned int last_draw = (total_work > gridDim.x ? total_work - gridDim.x : 0u) + gridDim.x - 1;
   int base = 0;  // key tiles this block has been through before the current item
   bool dead = false;  // a wait of this block ran out during an earlier item
 
   for (unsigned int work = blockIdx.x; work < total_work;) {
-    const int g = work % n_kv_heads;
-    const int tile = n_tiles_total - 1 - (int)((work / n_kv_heads) % n_tiles_total);
-    const int sub = work / n_kv_heads / n_tiles_total;
+    const int part = SPLIT ? work % parts : 0;
+    const unsigned int item = SPLIT ? work / parts : work;
+    const int g = item % n_kv_heads;
+    const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_tiles_total);
+    const int sub = item / n_kv_heads / n_tiles_total;
     const int b = tile_req[tile];
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     int n_tiles = 0;
+    if (SPLIT && part == 0 && tid == 0 && b < 0) split_flags[item] = 0;  // a padding tile: nothing to merge
 
     // (uniform over the block; after a wait ran out the block only draws its items, so that
     // the counter still returns to zero)
@@ -181,31 +215,47 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
 
       bool my_valid = false;
       int my_pos = -1;
-      if (softmax_thread) {
-        my_valid = row_valid(tid);
-        my_pos = my_valid ? pos[tok0 + row_token(tid)] : -1;
-        if (tid == 0) first_pos_s = my_pos;
-        // queries -> shared memory in the K-major operand layout (16-byte pieces, swizzled)
-        const __nv_bfloat16* src =
-            q + (size_t)(tok0 + row_token(tid)) * q_stride + (g * group + row_head(tid)) * HD;
+      // the softmax threads' rows: their positions, and the queries -> shared memory in the
+      // K-major operand layout (16-byte pieces, swizzled)
+      auto stage_queries = [&]() {
+        if (softmax_thread) {
+          my_valid = row_valid(tid);
+          my_pos = my_valid ? pos[tok0 + row_token(tid)] : -1;
+          if (tid == 0) first_pos_s = my_pos;
+          const __nv_bfloat16* src =
+              q + (size_t)(tok0 + row_token(tid)) * q_stride + (g * group + row_head(tid)) * HD;
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (my_valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-          *reinterpret_cast<uint4*>(Qs + (c / 8) * Q_HALF + fg_tma::swz(tid, c % 8)) = v;
+          for (int c = 0; c < HD / 8; ++c) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (my_valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(Qs + (c / 8) * Q_HALF + fg_tma::swz(tid, c % 8)) = v;
+          }
+          fence_async_smem();  // written by ordinary stores, read by the tensor core
         }
-        fence_async_smem();  // written by ordinary stores, read by the tensor core
-      }
-      __syncthreads();
-
-      const int min_pos = first_pos_s;  // tokens of a tile are consecutive positions
+        __syncthreads();
+      };
+      // a draw of a launch in parts first sees whether it has key tiles at all
+      if (!SPLIT) stage_queries();
+      const int min_pos = SPLIT ? pos[tok0] : first_pos_s;  // tokens of a tile are consecutive positions
       const int max_pos = min_pos + ntok - 1;
       const int k_begin = window > 0 ? max(0, min_pos - window + 1) : 0;
-      const int k_lo = k_begin / KEYS * KEYS;
       const int k_end = max_pos + 1;
-      n_tiles = (k_end - k_lo + KEYS - 1) / KEYS;
+      const int item_tiles = (k_end - k_begin / KEYS * KEYS + KEYS - 1) / KEYS;
+      // this part's key tiles: the item's are cut into stretches of equal length, at most `parts`
+      // of them (fewer where the rounded-up length leaves nothing for the last ones)
+      const int most_parts = SPLIT ? max(1, min(parts, item_tiles / SPLIT_MIN_TILES)) : 1;
+      const int tiles_per_part = (item_tiles + most_parts - 1) / most_parts;
+      const int n_parts = SPLIT ? (item_tiles + tiles_per_part - 1) / tiles_per_part : 1;
+      const int first_tile = part * tiles_per_part;
+      n_tiles = SPLIT ? max(0, min(tiles_per_part, item_tiles - first_tile)) : item_tiles;
+      const bool split = SPLIT && n_parts > 1;
+      const int k_lo = k_begin / KEYS * KEYS + first_tile * KEYS;
+      if (SPLIT && part == 0 && tid == 0) split_flags[item] = split ? n_parts : 0;
+      if (SPLIT && n_tiles > 0) stage_queries();  // (uniform over the block)
 
-      if (warp == LOAD_WARP) {
+      if (n_tiles == 0) {
+        // (nothing: the item has fewer parts than the launch gives every item)
+      } else if (warp == LOAD_WARP) {
         // ================================ load warp ================================
         // Keys and values of tile t go to the stage of its running number as soon as that
         // stage is free: the keys' once the S two tiles back is done, the values' once
@@ -447,24 +497,30 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const int gl = base + n_tiles - 1;
         mbar_wait(&o_done[gl & 1], (gl >> 1) & 1, status, &gave_up);
         tc_fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         __nv_bfloat16* dst =
             out + (size_t)(tok0 + row_token(tid)) * out_stride + (g * group + row_head(tid)) * HD;
+        if (!split) {
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll
-        for (int cc = 0; cc < HD / 32; ++cc) {
-          float part[32];
-          tmem_ld32(tmem + my_lane + COL_O + cc * 32, part);
-          if (my_valid) {
+          for (int cc = 0; cc < HD / 32; ++cc) {
+            float part_o[32];
+            tmem_ld32(tmem + my_lane + COL_O + cc * 32, part_o);
+            if (my_valid) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              v.x = pack_bf16(part[i] * inv, part[i + 1] * inv);
-              v.y = pack_bf16(part[i + 2] * inv, part[i + 3] * inv);
-              v.z = pack_bf16(part[i + 4] * inv, part[i + 5] * inv);
-              v.w = pack_bf16(part[i + 6] * inv, part[i + 7] * inv);
-              *reinterpret_cast<uint4*>(dst + cc * 32 + i) = v;
+              for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = pack_bf16(part_o[i] * inv, part_o[i + 1] * inv);
+                v.y = pack_bf16(part_o[i + 2] * inv, part_o[i + 3] * inv);
+                v.z = pack_bf16(part_o[i + 4] * inv, part_o[i + 5] * inv);
+                v.w = pack_bf16(part_o[i + 6] * inv, part_o[i + 7] * inv);
+                *reinterpret_cast<uint4*>(dst + cc * 32 + i) = v;
+              }
             }
           }
+        } else {
+          constexpr size_t SLOT = (size_t)ROWS * (HD + 2);
+          write_partial<HD>(tmem + my_lane + COL_O, split_scratch + ((size_t)item * parts + part) * SLOT + tid,
+                            m_ref == -INFINITY ? -INFINITY : m_ref * c, l_run);
         }
         tc_fence_before();
       }
@@ -492,6 +548,59 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   tc_fence_before();
   __syncthreads();
   if (warp == LOAD_WARP) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// Adds up the parts of the items that attention_prefill_tc5_kernel worked on in parts:
+// block (x, item) takes MERGE_THREADS of the item's ROWS * HD / 8 (row, 8 columns) pieces,
+// rows running fastest, so that a warp reads neighbouring floats of a partial.  The parts are
+// weighed by their reference maxima and summed in their order.
+constexpr int MERGE_THREADS = 256;
+
+template <int HD>
+__global__ void __launch_bounds__(MERGE_THREADS)
+attention_prefill_merge_kernel(const float* split_scratch, const int* split_flags, int parts, __nv_bfloat16* out,
+                               int out_stride, const int* tile_tok0, const int* tile_ntok, int n_tiles_total,
+                               int n_kv_heads, int group, int heads_per_block) {
+  pdl_wait();
+  const unsigned int item = blockIdx.y;
+  const int n_parts = (int)ld_global_4(split_flags + item);
+  if (n_parts <= 1) return;
+  const int piece = blockIdx.x * MERGE_THREADS + threadIdx.x;
+  const int row = piece % ROWS, col0 = piece / ROWS * 8;
+  if (col0 >= HD) return;
+  const int g = item % n_kv_heads;
+  const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_tiles_total);
+  const int sub = item / n_kv_heads / n_tiles_total;
+  const int token = row / heads_per_block, head = sub * heads_per_block + row % heads_per_block;
+  if (token >= tile_ntok[tile] || head >= group) return;
+  constexpr size_t SLOT = (size_t)ROWS * (HD + 2);
+  const float* slots = split_scratch + (size_t)item * parts * SLOT;
+  float m_all = -INFINITY;
+  for (int p = 0; p < n_parts; ++p) m_all = fmaxf(m_all, __ldcg(slots + p * SLOT + (size_t)HD * ROWS + row));
+  // the weight of part p (a part that saw no key has -inf and weighs nothing)
+  auto weight = [&](int p) {
+    const float m_p = __ldcg(slots + p * SLOT + (size_t)HD * ROWS + row);
+    return m_p == -INFINITY ? 0.f : exp2f(m_p - m_all);
+  };
+  float l_all = 0.f;
+  for (int p = 0; p < n_parts; ++p) l_all += __ldcg(slots + p * SLOT + (size_t)(HD + 1) * ROWS + row) * weight(p);
+  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
+  for (int p = 0; p < n_parts; ++p) {
+    const float w = weight(p) * inv;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __ldcg(slots + p * SLOT + (size_t)(col0 + i) * ROWS + row) * w;
+  }
+  uint4 v;
+  v.x = pack_bf16(acc[0], acc[1]);
+  v.y = pack_bf16(acc[2], acc[3]);
+  v.z = pack_bf16(acc[4], acc[5]);
+  v.w = pack_bf16(acc[6], acc[7]);
+  __nv_bfloat16* dst = out + (size_t)(tile_tok0[tile] + token) * out_stride + (g * group + head) * HD + col0;
+  *reinterpret_cast<uint4*>(dst) = v;
 }
 
 }  // namespace fg_tc5

@@ -64,7 +64,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _P, _P, _P],
+                                      _I, _F, _P, _P, _P, _I, _I, _P, _P],
+    "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P],
     "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
@@ -201,11 +202,27 @@ class Ops:
         self._scratch = {}
         # the prompt attention kernel's blocks draw their work from it; zero between launches
         self._work_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # head size -> (partials, flags, (item, part) pairs they hold) of prompt-attention launches
+        # that work on their long items in several parts; buffers that were outgrown stay alive, since
+        # captured graphs may hold their addresses
+        self._split = {}
+        self._split_retired = []
         self.use_tcgen05 = not bool(os.environ.get("FG_NO_TCGEN05"))
         # library products accumulate and reduce in float32 (no bfloat16 split-K sums)
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
     # -- status word ---------------------------------------------------------
+    def clear_status(self) -> None:
+        """Zero the status word after a recorded fault, and with it what a kernel whose wait
+        ran out may have left behind between launches: the prompt attention's work counter
+        and the flags of its split items."""
+        self.status.zero_()
+        self._work_counter.zero_()
+        for _scratch, flags, _room in self._split.values():
+            flags.zero_()
+        for _scratch, flags in self._split_retired:
+            flags.zero_()
+
     def check_status(self) -> None:
         """Read the device status word (synchronises) and raise if a kernel
         recorded a fault instead of performing a bad access."""
@@ -385,6 +402,21 @@ class Ops:
                 maps.append(tm)
         return tuple(maps)
 
+    def _split_buffers(self, head_dim: int, items: int):
+        """Partials and flags for a prompt-attention launch that wants to work on its long
+        items in parts, ``items`` (item, part) pairs in all (0: it does not).  They grow to the largest launch seen, outside
+        graph captures only: a capture that finds them too small records a launch that does
+        not split."""
+        scratch, flags, room = self._split.get(head_dim, (None, None, 0))
+        if items > room and not torch.cuda.is_current_stream_capturing():
+            if room:
+                self._split_retired.append((scratch, flags))
+            room = max(items, 2 * room)
+            scratch = torch.empty(room * PREFILL_TMA_ROWS * (head_dim + 2), dtype=torch.float32, device=self.device)
+            flags = torch.zeros(room, dtype=torch.int32, device=self.device)
+            self._split[head_dim] = (scratch, flags, room)
+        return scratch, flags, room
+
     def attention(self, q, out, memory, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
                   window: Optional[int], scale: float) -> None:
         """Paged causal attention of the step's query tokens; ``memory`` is the
@@ -417,8 +449,14 @@ class Ops:
                     page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
                     _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale))
             if head_dim in (64, 128) and self.use_tcgen05:
+                want = lib.fg_attention_prefill_tc5_split_slots(
+                    tiles.n, n_heads, n_kv_heads, -1 if tiles.max_keys is None else tiles.max_keys)
+                scratch, flags, room = self._split_buffers(head_dim, want)
                 _check(lib, lib.fg_attention_prefill_tc5_bf16(
-                    *args, _ptr(self._work_counter), _ptr(self.status), _stream()))
+                    *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room,
+                    -1 if tiles.max_keys is None else tiles.max_keys, _ptr(self.status), _stream()))
+                if 0 < want <= room:
+                    Ops.launches += 1  # the kernel that adds up the parts of split items
             else:
                 _check(lib, lib.fg_attention_prefill_tma_bf16(*args, _ptr(self.status), _stream()))
         elif tiles.n:

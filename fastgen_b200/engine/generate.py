@@ -341,7 +341,7 @@ class Fastgen:
         cleared, the others go on."""
         message = describe_status(word)
         logger.error("%s; ending %d request(s) of the step", message, len(reqs))
-        self.ops.status.zero_()
+        self.ops.clear_status()
         for req in self.scheduler.fail(reqs, message):
             yield self._packet(req)
 

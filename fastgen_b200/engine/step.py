@@ -40,12 +40,15 @@ class StepEntry:
 
 @dataclass
 class AttentionTiles:
-    """Device arrays that cut the step's tokens into attention tiles."""
+    """Device arrays that cut the step's tokens into attention tiles; ``max_keys`` is the
+    most keys one of them reads where the host knows it (a captured graph serves every
+    length and says ``None``)."""
 
     req: torch.Tensor
     tok0: torch.Tensor
     ntok: torch.Tensor
     n: int
+    max_keys: Optional[int] = None
 
 
 @dataclass
@@ -141,7 +144,7 @@ class StepContext:
         if n == 0:
             return AttentionTiles(None, None, None, 0)
         packed = torch.tensor(req + tok0 + ntok, dtype=torch.int32).to(self.device)
-        return AttentionTiles(packed[:n], packed[n : 2 * n], packed[2 * n :], n)
+        return AttentionTiles(packed[:n], packed[n : 2 * n], packed[2 * n :], n, tiles[-1][0])
 
     def single_tokens(self) -> "SingleTokens":
         """The sequences that bring exactly one token (decoded tokens)."""

@@ -85,7 +85,8 @@ def main(argv=None) -> int:
     prompts = [tuple(int(x) for x in p.split(",")) for p in args.prompt]
     singles = [tuple(int(x) for x in s.split(",")) for s in args.single]
     if not prompts and not singles:
-        prompts = [(512, 0), (2048, 0), (8192, 0), (2048, 8192), (512, 16384), (8192, 32768)]
+        prompts = [(512, 0), (2048, 0), (8192, 0), (2048, 8192), (512, 16384), (8192, 32768), (256, 32768), (64, 32768),
+                   (8, 32768)]
         singles = [(1, 4096), (8, 4096), (64, 4096), (1, 65536), (8, 65536)]
     for hd in args.head_dim or [128, 64]:
         for t, cached in prompts:

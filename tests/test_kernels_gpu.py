@@ -437,6 +437,42 @@ def test_attention_window_edge_tiled(ops16, hd, hq, hkv, page):
                     _sharp(ops16, seqs, hq, hkv, hd, page, window, far, seed=5)
 
 
+@pytest.mark.parametrize("hd,hq,hkv,page", [(128, 8, 2, 64), (64, 6, 2, 16), (128, 4, 1, 256), (64, 24, 2, 64)])
+def test_attention_long_items_in_parts(ops16, hd, hq, hkv, page):
+    """A launch of few (query tile, head) items works on an item of 16 key tiles or more in several
+    parts and adds them up in a second kernel.  The dominant key lies at the first and last key of
+    the parts (with 2,040 keys and 8 tiles a part: 512 keys each), the other requests of the call
+    are long, short (not split) and of few tokens; with a window the parts start at its edge."""
+
+    def parts_seen():
+        # the kernel leaves the number of parts of every item of its last launch
+        if hd not in ops16._split:
+            return set()
+        flags = ops16._split[hd][1]
+        seen = set(flags.tolist()) - {0}
+        flags.zero_()
+        return seen
+
+    parts_seen()  # (forget what earlier tests left)
+    for far in (0, 511, 512, 1023, 1024, 1535, 1536, 2039):
+        _sharp(ops16, [(2000, 40)], hq, hkv, hd, page, None, far)
+    assert parts_seen() == {4}  # 32 key tiles: four parts of 8
+    for far in (0, 700, 1472, 2700, 3008):
+        _sharp(ops16, [(1500, 100), (3000, 9), (100, 30)], hq, hkv, hd, page, None, far)
+    assert parts_seen() == {3, 6}  # 25 and 48 key tiles; the short request's items are not split
+    for far in (3008 - 1100, 3008 - 1100 + 1, 2500):
+        _sharp(ops16, [(3000, 9), (1200, 2)], hq, hkv, hd, page, 1100, far, seed=5)
+    assert parts_seen() == {2}  # 19 and 18 key tiles from the window's edge on
+    # random values, against the plain reference under the rule of the other cases
+    out, ref = _attention_case(ops16, [(4000, 70), (1000, 3)], hq, hkv, hd, page, None, seed=3, runs=2, layer=1)
+    assert float((out - ref).abs().max()) < 2e-2
+    parts_seen()
+    # 97 key tiles for up to 32 parts of at least 8: 12 parts of 9 tiles would leave the last one empty
+    out, ref = _attention_case(ops16, [(6145, 60)], hq, hkv, hd, page, None, seed=4, runs=2, layer=1)
+    assert float((out - ref).abs().max()) < 2e-2
+    assert parts_seen() == {11}
+
+
 @pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 300])
 def test_attention_reaches_a_far_key(ops32, ops16, far):
     """One key among hundreds dominates the last query: it must be found wherever it lies."""

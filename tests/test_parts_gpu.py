@@ -631,11 +631,13 @@ def test_first_tokens(tmp_path, dtype):
     H.compare(model_dir, reqs, H.collect(steps, outputs), dtype)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_long_prompt_in_large_portions(tmp_path, dtype):
+@pytest.mark.parametrize("dtype,step_graphs", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+def test_long_prompt_in_large_portions(tmp_path, dtype, step_graphs):
     """A prompt of thousands of tokens in portions of thousands (dozens of key tiles a query
-    tile, llama3-scaled angles beyond the original context), then single tokens over dozens
-    of key splits."""
+    tile, llama3-scaled angles beyond the original context), then in portions of a hundred and
+    of a dozen tokens on thousands of cached keys (few items with many key tiles each, which the
+    bfloat16 prompt kernel works on in parts), then single tokens over dozens of key splits;
+    eagerly and with the portions' steps replayed from captured graphs."""
     cfg = dict(
         architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_size=344, num_hidden_layers=2,
         num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, vocab_size=300, tie_word_embeddings=False,
@@ -649,16 +651,20 @@ def test_long_prompt_in_large_portions(tmp_path, dtype):
     toks = H.random_tokens(300, n, 1)
     head = n - 6
     steps, p = [], 0
-    for chunk in (3000, 2048, head - 5048):
+    for chunk in (3000, 2048, 1000, 130, 2, head - 6180):
         steps.append(dict(step=len(steps), entries=[dict(id="a", tokens=toks[p:p + chunk], want=[0, chunk // 2, chunk - 1])],
                           end=[]))
         p += chunk
+    assert p == head
     for p in range(head, n):
         steps.append(dict(step=len(steps), entries=[dict(id="a", tokens=[toks[p]], want=[0])], end=[]))
-    outputs, _ = H.run_engine(model_dir, dtype, steps, page_size=64, max_tokens=8192)
+    outputs, engine = H.run_engine(model_dir, dtype, steps, page_size=64, max_tokens=8192,
+                                   max_step_tokens=3072 if step_graphs else None)
+    if step_graphs:
+        assert engine.step_graphs is not None and engine.step_graphs.replays >= 5
     got = H.collect(steps, outputs)["a"]
     ref = H.plain_logits(model_dir, toks)
-    assert len(got) == 9 + 6
+    assert len(got) == 3 * 6 - 1 + 6  # (the portion of two tokens has two places)
     for p, row in got.items():
         H.check_row(row, ref[p], dtype, f"pos {p}")
 
