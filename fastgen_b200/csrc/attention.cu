@@ -327,6 +327,13 @@ extern "C" int fg_attention_prefill_tc5_supported() { return 1; }
 // for, or 0 if it would not split: too many items, or, where the host knows the most keys an
 // item reads (`max_keys`, else -1), too few keys for a second part.  With null pointers or
 // less room (`split_slots`) the launch does not split either.
+//
+// `real_tiles` (may be null) points at the number of tiles at the end of the list that are
+// real, for a launch that is captured in a graph whose list has padding in front
+// (`nominal_tiles` in fg_attention_prefill_tc5_split_slots: the tiles of a step of the graph's
+// token count that holds prompt tokens only; 0 without such a list): the kernel then hands out
+// the real tiles only and chooses the number of parts itself, which asks for room for one pair
+// a block.
 static long long tc5_items(int n_tiles, int n_heads, int n_kv_heads) {
   const int group = n_heads / n_kv_heads;
   const int hpb = group < fg_tc5::ROWS ? group : fg_tc5::ROWS;
@@ -338,10 +345,14 @@ static int tc5_parts(long long items) {
   return (int)(parts < 1 ? 1 : parts > fg_tc5::MAX_PARTS ? fg_tc5::MAX_PARTS : parts);
 }
 
-extern "C" int fg_attention_prefill_tc5_split_slots(int n_tiles, int n_heads, int n_kv_heads, int max_keys) {
+extern "C" int fg_attention_prefill_tc5_split_slots(int n_tiles, int n_heads, int n_kv_heads, int max_keys,
+                                                    int nominal_tiles) {
   if (n_tiles <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return 0;
   // an item is split from 2 * SPLIT_MIN_TILES key tiles on
   if (max_keys >= 0 && max_keys <= (2 * fg_tc5::SPLIT_MIN_TILES - 1) * fg_tc5::KEYS) return 0;
+  // (with padding in the list: the instantiation that can split, unless a step whose tokens
+  // are all prompt tokens, `nominal_tiles` tiles, would fill the launch's blocks anyway)
+  if (nominal_tiles > 0) return tc5_items(nominal_tiles, n_heads, n_kv_heads) < 2ll * sm_count() ? 2 * sm_count() : 0;
   const long long items = tc5_items(n_tiles, n_heads, n_kv_heads);
   const int parts = tc5_parts(items);
   return parts > 1 ? (int)(items * parts) : 0;
@@ -354,7 +365,8 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
                                              const int* tile_tok0, const int* tile_ntok, int n_tiles,
                                              int n_heads, int n_kv_heads, int head_dim, int window, float scale,
                                              unsigned int* work_counter, float* split_scratch, int* split_flags,
-                                             int split_slots, int max_keys, int* status, cudaStream_t stream) {
+                                             int split_slots, int max_keys, const int* real_tiles, int nominal_tiles,
+                                             int* status, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   FG_CHECK_ARG(work_counter != nullptr, "fg_attention_prefill_tc5_bf16: no work counter");
   FG_CHECK_ARG(head_dim == FG_HEAD_DIM, "fg_attention_prefill_tc5_bf16: library built for head size %d, got %d",
@@ -383,32 +395,37 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
   // two blocks an SM take the (tile, kv head, slice of the group) items from a counter
   const long long items = tc5_items(n_tiles, n_heads, n_kv_heads);
   FG_CHECK_ARG(items < (1ll << 30), "fg_attention_prefill_tc5_bf16: %lld work items in one call", items);
-  const int want = fg_attention_prefill_tc5_split_slots(n_tiles, n_heads, n_kv_heads, max_keys);
-  const int parts = (want > 0 && split_scratch && split_flags && want <= split_slots) ? tc5_parts(items) : 1;
+  const int want = fg_attention_prefill_tc5_split_slots(n_tiles, n_heads, n_kv_heads, max_keys,
+                                                        real_tiles ? (nominal_tiles > 0 ? nominal_tiles : 1) : 0);
+  const bool split = want > 0 && split_scratch && split_flags && want <= split_slots;
+  const int parts = split && !real_tiles ? tc5_parts(items) : 1;
   const long long total = items * parts;
   const long long resident = 2ll * sm_count();
-  const int grid = (int)(total < resident ? total : resident);
-  (parts > 1 ? kern_parts : kern_whole)<<<grid, fg_tc5::THREADS, smem, stream>>>(
+  // (a launch that chooses its parts itself has all its blocks)
+  const int grid = (int)(split && real_tiles ? resident : total < resident ? total : resident);
+  (split ? kern_parts : kern_whole)<<<grid, fg_tc5::THREADS, smem, stream>>>(
       km, vm, layer, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, block_table, table_width,
       page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
-      scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, status);
+      scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots, real_tiles, status);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
-  if (parts > 1) {
-    dim3 mgrid(fg_tc5::ROWS * (FG_HEAD_DIM / 8) / fg_tc5::MERGE_THREADS, (unsigned int)items);
+  if (split) {
+    // (an item has a second part only if the launch has two blocks for it)
+    const long long most = items < resident / 2 ? items : resident / 2;
+    dim3 mgrid(fg_tc5::ROWS * (FG_HEAD_DIM / 8) / fg_tc5::MERGE_THREADS, (unsigned int)(most > 0 ? most : 1));
     fg_launch_pdl(fg_tc5::attention_prefill_merge_kernel<FG_HEAD_DIM>, mgrid, dim3(fg_tc5::MERGE_THREADS), 0, stream,
                   (const float*)split_scratch, (const int*)split_flags, parts, (__nv_bfloat16*)out, out_stride,
-                  tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb);
+                  tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, grid, split_slots, real_tiles);
     FG_CHECK_LAUNCH("fg_attention_prefill_merge");
   }
   return 0;
 }
 #else
 extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
-extern "C" int fg_attention_prefill_tc5_split_slots(int, int, int, int) { return 0; }
+extern "C" int fg_attention_prefill_tc5_split_slots(int, int, int, int, int) { return 0; }
 #endif
 #else
 extern "C" int fg_attention_decode_tma_supported() { return 0; }
 extern "C" int fg_attention_prefill_tc5_supported() { return 0; }
-extern "C" int fg_attention_prefill_tc5_split_slots(int, int, int, int) { return 0; }
+extern "C" int fg_attention_prefill_tc5_split_slots(int, int, int, int, int) { return 0; }
 extern "C" int fg_attention_decode_is_persistent(int, int, int, int) { return 0; }
 #endif

@@ -88,6 +88,31 @@ constexpr size_t smem_bytes() {
 }
 constexpr int TMEM_COLS = 256;  // S0, S1 (64 columns each; P overwrites its S) + O (HD <= 128)
 
+// How a launch hands its work out.  `real_tiles` (null: all of them) points at the number of
+// tiles at the end of the tile list that are real; a captured graph's list has padding entries
+// in front of them, their number changes from replay to replay, and the host cannot choose the
+// number of parts a launch ahead.  The kernel then chooses it: as many as the launch's blocks
+// allow, given the real items, and the partials have room for.
+struct HandOut {
+  int n_real;  // tiles that are handed out, the last ones of the list
+  int parts;   // draws an item
+};
+__device__ __forceinline__ HandOut hand_out(const int* real_tiles, int n_tiles_total, int n_kv_heads, int n_subs,
+                                            int parts_given, int main_grid, int split_slots, bool split) {
+  HandOut h;
+  h.n_real = n_tiles_total;
+  h.parts = split ? parts_given : 1;
+  if (real_tiles) {
+    h.n_real = min(max((int)ld_global_4(real_tiles), 0), n_tiles_total);
+    if (split) {
+      const long long items = (long long)h.n_real * n_kv_heads * n_subs;
+      h.parts = items > 0 ? (int)min((long long)MAX_PARTS, max(1ll, main_grid / items)) : 1;
+      if (items * h.parts > split_slots) h.parts = 1;
+    }
+  }
+  return h;
+}
+
 // The partial of one part of a split item: this thread's row of O (tensor memory, unnormalised),
 // its reference maximum (in units of log2) and its row sum, to [column][row] in `slot` (which
 // already points at the row), so that a warp's rows are neighbours.  Not inlined: the kernel's
@@ -117,7 +142,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              const int* __restrict__ tile_req, const int* __restrict__ tile_tok0,
                              const int* __restrict__ tile_ntok, int n_tiles_total, int n_kv_heads, int group,
                              int heads_per_block, int window, float scale_log2, unsigned int* work_counter,
-                             int parts, float* split_scratch, int* split_flags, int* status) {
+                             int parts, float* split_scratch, int* split_flags, int split_slots,
+                             const int* real_tiles, int* status) {
   static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
   constexpr int HALVES = HD / 64;
   constexpr int STAGE_BYTES = HALVES * KV_HALF;
@@ -189,8 +215,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // `split_flags[item]` says how many parts there are (0: the item wrote its output itself);
   // attention_prefill_merge_kernel, launched behind this one, adds the partials up.
   const unsigned int n_subs = (group + heads_per_block - 1) / heads_per_block;
-  if (!SPLIT) parts = 1;
-  const unsigned int total_work = (unsigned int)n_tiles_total * n_kv_heads * n_subs * parts;
+  const HandOut ho = hand_out(real_tiles, n_tiles_total, n_kv_heads, n_subs, parts, gridDim.x, split_slots, SPLIT);
+  const int n_real = ho.n_real;
+  parts = ho.parts;
+  const unsigned int total_work = (unsigned int)n_real * n_kv_heads * n_subs * parts;
   const unsigned int last_draw = (total_work > gridDim.x ? total_work - gridDim.x : 0u) + gridDim.x - 1;
   int base = 0;  // key tiles this block has been through before the current item
   bool dead = false;  // a wait of this block ran out during an earlier item
@@ -199,12 +227,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int part = SPLIT ? work % parts : 0;
     const unsigned int item = SPLIT ? work / parts : work;
     const int g = item % n_kv_heads;
-    const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_tiles_total);
-    const int sub = item / n_kv_heads / n_tiles_total;
+    const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_real);
+    const int sub = item / n_kv_heads / n_real;
     const int b = tile_req[tile];
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     int n_tiles = 0;
-    if (SPLIT && part == 0 && tid == 0 && b < 0) split_flags[item] = 0;  // a padding tile: nothing to merge
+    if (SPLIT && parts > 1 && part == 0 && tid == 0 && b < 0) split_flags[item] = 0;  // a padding tile: nothing to merge
 
     // (uniform over the block; after a wait ran out the block only draws its items, so that
     // the counter still returns to zero)
@@ -250,7 +278,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       n_tiles = SPLIT ? max(0, min(tiles_per_part, item_tiles - first_tile)) : item_tiles;
       const bool split = SPLIT && n_parts > 1;
       const int k_lo = k_begin / KEYS * KEYS + first_tile * KEYS;
-      if (SPLIT && part == 0 && tid == 0) split_flags[item] = split ? n_parts : 0;
+      if (SPLIT && parts > 1 && part == 0 && tid == 0) split_flags[item] = split ? n_parts : 0;
       if (SPLIT && n_tiles > 0) stage_queries();  // (uniform over the block)
 
       if (n_tiles == 0) {
@@ -560,17 +588,23 @@ template <int HD>
 __global__ void __launch_bounds__(MERGE_THREADS)
 attention_prefill_merge_kernel(const float* split_scratch, const int* split_flags, int parts, __nv_bfloat16* out,
                                int out_stride, const int* tile_tok0, const int* tile_ntok, int n_tiles_total,
-                               int n_kv_heads, int group, int heads_per_block) {
+                               int n_kv_heads, int group, int heads_per_block, int main_grid, int split_slots,
+                               const int* real_tiles) {
   pdl_wait();
   const unsigned int item = blockIdx.y;
+  const int n_subs = (group + heads_per_block - 1) / heads_per_block;
+  const HandOut ho = hand_out(real_tiles, n_tiles_total, n_kv_heads, n_subs, parts, main_grid, split_slots, true);
+  const int n_real = ho.n_real;
+  parts = ho.parts;
+  if (parts <= 1 || item >= (unsigned int)(n_real * n_kv_heads * n_subs)) return;
   const int n_parts = (int)ld_global_4(split_flags + item);
   if (n_parts <= 1) return;
   const int piece = blockIdx.x * MERGE_THREADS + threadIdx.x;
   const int row = piece % ROWS, col0 = piece / ROWS * 8;
   if (col0 >= HD) return;
   const int g = item % n_kv_heads;
-  const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_tiles_total);
-  const int sub = item / n_kv_heads / n_tiles_total;
+  const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_real);
+  const int sub = item / n_kv_heads / n_real;
   const int token = row / heads_per_block, head = sub * heads_per_block + row % heads_per_block;
   if (token >= tile_ntok[tile] || head >= group) return;
   constexpr size_t SLOT = (size_t)ROWS * (HD + 2);

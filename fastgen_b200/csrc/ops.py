@@ -64,8 +64,8 @@ _ATTN_SIGNATURES = {
     "fg_attention_prefill_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _P, _P],
     "fg_attention_prefill_tc5_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _P, _P, _P, _I, _I, _P, _P],
-    "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I],
+                                      _I, _F, _P, _P, _P, _I, _I, _P, _I, _P, _P],
+    "fg_attention_prefill_tc5_split_slots": [_I, _I, _I, _I, _I],
     "fg_attention_decode_tma_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I,
                                      _F, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _P, _P],
     "fg_attention_decode_is_persistent": [_I, _I, _I, _I],
@@ -440,7 +440,8 @@ class Ops:
             return
         use_tma = memory.tensor_maps is not None
         rows = PREFILL_TMA_ROWS if use_tma else PREFILL_ROWS
-        tiles = ctx.attention_tiles(attention_tiling(n_heads, n_kv_heads, rows), 2)
+        tiling = attention_tiling(n_heads, n_kv_heads, rows)
+        tiles = ctx.attention_tiles(tiling, 2)
         if tiles.n and use_tma:
             # head sizes 64 and 128: tcgen05.mma with S and O in tensor memory; other
             # multiples of 64: mma.sync on the same TMA tiles (FG_NO_TCGEN05=1 forces that)
@@ -449,12 +450,14 @@ class Ops:
                     page_size, k_pages.shape[0], _ptr(ctx.pos), _ptr(tiles.req), _ptr(tiles.tok0),
                     _ptr(tiles.ntok), tiles.n, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale))
             if head_dim in (64, 128) and self.use_tcgen05:
-                want = lib.fg_attention_prefill_tc5_split_slots(
-                    tiles.n, n_heads, n_kv_heads, -1 if tiles.max_keys is None else tiles.max_keys)
+                max_keys = -1 if tiles.max_keys is None else tiles.max_keys
+                # a captured list has padding: what a step of prompt tokens only would hold
+                nominal = 0 if tiles.count is None else max(1, -(-q.shape[0] // tiling))
+                want = lib.fg_attention_prefill_tc5_split_slots(tiles.n, n_heads, n_kv_heads, max_keys, nominal)
                 scratch, flags, room = self._split_buffers(head_dim, want)
                 _check(lib, lib.fg_attention_prefill_tc5_bf16(
-                    *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room,
-                    -1 if tiles.max_keys is None else tiles.max_keys, _ptr(self.status), _stream()))
+                    *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room, max_keys,
+                    _ptr(tiles.count), nominal, _ptr(self.status), _stream()))
                 if 0 < want <= room:
                     Ops.launches += 1  # the kernel that adds up the parts of split items
             else:

@@ -42,13 +42,16 @@ class StepEntry:
 class AttentionTiles:
     """Device arrays that cut the step's tokens into attention tiles; ``max_keys`` is the
     most keys one of them reads where the host knows it (a captured graph serves every
-    length and says ``None``)."""
+    length and says ``None``).  A captured graph's lists have room for the most tiles a step
+    of its shape can have, with the real ones at the end (padding entries have request -1);
+    ``count`` is then a device int that says how many are real in this replay."""
 
     req: torch.Tensor
     tok0: torch.Tensor
     ntok: torch.Tensor
     n: int
     max_keys: Optional[int] = None
+    count: Optional[torch.Tensor] = None
 
 
 @dataclass

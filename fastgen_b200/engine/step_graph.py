@@ -65,7 +65,7 @@ class _Shape:
                         ("single_req", n_singles), ("single_tok", n_singles)):
             self.off[name] = self.size
             self.size += n
-        self.capacity = self.size + 3 * 4 * (n_tokens + max_seqs + 8)  # room for four tile lists
+        self.capacity = self.size + 3 * 4 * (n_tokens + max_seqs + 8) + 4  # room for four tile lists
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
         self.ring = [torch.zeros(self.capacity, dtype=torch.int32).pin_memory() for _ in range(_RING)]
         self.ring_events: List[Optional[torch.cuda.Event]] = [None] * _RING
@@ -85,15 +85,15 @@ class _Shape:
                 raise RuntimeError(f"a captured step asked for a tile list {key} that its capture did not")
             # every sequence may end with a partial tile
             cap = -(-self.n_tokens // tokens_per_tile) + self.max_seqs
-            if self.size + 3 * cap > self.capacity:
+            if self.size + 3 * cap + 1 > self.capacity:
                 raise RuntimeError("too many kinds of attention tiles in one step")
             self.tile_keys[key] = self.size
             self.tile_capacity[key] = cap
             self.dev[self.size : self.size + cap] = -1  # until a step fills them: no tile has a request
-            self.size += 3 * cap
+            self.size += 3 * cap + 1  # requests, first tokens, numbers of tokens, and how many tiles are real
         o, cap = self.tile_keys[key], self.tile_capacity[key]
         return AttentionTiles(self.dev[o : o + cap], self.dev[o + cap : o + 2 * cap], self.dev[o + 2 * cap : o + 3 * cap],
-                              cap)
+                              cap, None, self.dev[o + 3 * cap : o + 3 * cap + 1])
 
     def context(self) -> StepContext:
         ctx = StepContext(self.device)
@@ -190,6 +190,7 @@ class StepGraphs:
                 host[off + cap - k : off + cap] = [tile[1] for tile in tiles]
                 host[off + 2 * cap - k : off + 2 * cap] = [tile[2] for tile in tiles]
                 host[off + 3 * cap - k : off + 3 * cap] = [tile[3] for tile in tiles]
+            host[off + 3 * cap] = k
         sh.dev[: sh.size].copy_(staging[: sh.size], non_blocking=True)
         self.last_h2d_bytes = 4 * sh.size
         ev = torch.cuda.Event()
