@@ -321,8 +321,8 @@ extern "C" int fg_attention_prefill_tc5_supported() { return 1; }
 //
 // A launch of fewer items than resident blocks works on its long items in several parts (see
 // the kernel).  That needs, for every (item, part), fg_tc5::ROWS * (head size + 2) floats of
-// `split_scratch`, and an int of `split_flags` for every item (the kernel writes there in how
-// many parts it worked on the item; a second kernel adds the parts up).
+// `split_scratch`, and two ints of `split_flags` for every item, zero before the first launch
+// (the kernel leaves the counter so).
 // fg_attention_prefill_tc5_split_slots says how many (item, part) pairs a launch wants room
 // for, or 0 if it would not split: too many items, or, where the host knows the most keys an
 // item reads (`max_keys`, else -1), too few keys for a second part.  With null pointers or
@@ -397,10 +397,10 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
   FG_CHECK_ARG(items < (1ll << 30), "fg_attention_prefill_tc5_bf16: %lld work items in one call", items);
   const int want = fg_attention_prefill_tc5_split_slots(n_tiles, n_heads, n_kv_heads, max_keys,
                                                         real_tiles ? (nominal_tiles > 0 ? nominal_tiles : 1) : 0);
+  const long long resident = 2ll * sm_count();
   const bool split = want > 0 && split_scratch && split_flags && want <= split_slots;
   const int parts = split && !real_tiles ? tc5_parts(items) : 1;
   const long long total = items * parts;
-  const long long resident = 2ll * sm_count();
   // (a launch that chooses its parts itself has all its blocks)
   const int grid = (int)(split && real_tiles ? resident : total < resident ? total : resident);
   (split ? kern_parts : kern_whole)<<<grid, fg_tc5::THREADS, smem, stream>>>(
@@ -408,15 +408,6 @@ extern "C" int fg_attention_prefill_tc5_bf16(const void* q, int q_stride, void* 
       page_size, n_pages, pos, tile_req, tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, window,
       scale * 1.4426950408889634f, work_counter, parts, split_scratch, split_flags, split_slots, real_tiles, status);
   FG_CHECK_LAUNCH("fg_attention_prefill_tc5_bf16");
-  if (split) {
-    // (an item has a second part only if the launch has two blocks for it)
-    const long long most = items < resident / 2 ? items : resident / 2;
-    dim3 mgrid(fg_tc5::ROWS * (FG_HEAD_DIM / 8) / fg_tc5::MERGE_THREADS, (unsigned int)(most > 0 ? most : 1));
-    fg_launch_pdl(fg_tc5::attention_prefill_merge_kernel<FG_HEAD_DIM>, mgrid, dim3(fg_tc5::MERGE_THREADS), 0, stream,
-                  (const float*)split_scratch, (const int*)split_flags, parts, (__nv_bfloat16*)out, out_stride,
-                  tile_tok0, tile_ntok, n_tiles, n_kv_heads, group, hpb, grid, split_slots, real_tiles);
-    FG_CHECK_LAUNCH("fg_attention_prefill_merge");
-  }
   return 0;
 }
 #else

@@ -44,7 +44,7 @@ constexpr int KV_HALF = KEYS * 128;   // bytes of one 64-element half of a K or 
 constexpr int Q_HALF = ROWS * 128;    // ... of the Q tile
 constexpr float RESCALE_THRESHOLD = 8.f;  // in units of log2
 constexpr int SPLIT_MIN_TILES = 8;        // fewest key tiles of a part of a split item
-constexpr int MAX_PARTS = 32;             // most parts of an item
+constexpr int MAX_PARTS = 16;             // most parts of an item (one block adds them up)
 
 // 2^x as the special-function unit gives it (relative error about 2^-22, results below
 // 2^-126 flushed to zero): the probabilities are rounded to bfloat16 right after, and
@@ -130,6 +130,47 @@ __device__ __noinline__ void write_partial(uint32_t o_addr, float* slot, float m
   __stcg(slot + (size_t)(HD + 1) * ROWS, l);
 }
 
+// This thread's row of a split item: the parts' partials, weighed by their reference maxima
+// and summed in the order of the parts, normalised, to `dst` (the row's output).  `slots`
+// points at the row in the first part's partial.
+template <int HD>
+__device__ __noinline__ void merge_parts(const float* slots, int n_parts, __nv_bfloat16* dst, bool valid) {
+  constexpr size_t SLOT = (size_t)ROWS * (HD + 2);
+  float m_all = -INFINITY;
+  for (int p = 0; p < n_parts; ++p) m_all = fmaxf(m_all, __ldcg(slots + p * SLOT + (size_t)HD * ROWS));
+  // the weight of part p (a part that saw no key has -inf and weighs nothing)
+  auto weight = [&](int p) {
+    const float m_p = __ldcg(slots + p * SLOT + (size_t)HD * ROWS);
+    return m_p == -INFINITY ? 0.f : exp2f(m_p - m_all);
+  };
+  float l_all = 0.f;
+  for (int p = 0; p < n_parts; ++p) l_all += __ldcg(slots + p * SLOT + (size_t)(HD + 1) * ROWS) * weight(p);
+  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+#pragma unroll 1
+  for (int cc = 0; cc < HD / 16; ++cc) {
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+#pragma unroll 2
+    for (int p = 0; p < n_parts; ++p) {
+      const float w = weight(p) * inv;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] += __ldcg(slots + p * SLOT + (size_t)(cc * 16 + i) * ROWS) * w;
+    }
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 8) {
+        uint4 v;
+        v.x = pack_bf16(acc[i], acc[i + 1]);
+        v.y = pack_bf16(acc[i + 2], acc[i + 3]);
+        v.z = pack_bf16(acc[i + 4], acc[i + 5]);
+        v.w = pack_bf16(acc[i + 6], acc[i + 7]);
+        *reinterpret_cast<uint4*>(dst + cc * 16 + i) = v;
+      }
+    }
+  }
+}
+
 // SPLIT: the instantiation for launches that work on long items in parts (`parts` > 1); the
 // other one has none of that code (its main loop proved sensitive to it: head size 64 ran 5 %
 // slower with it).
@@ -165,6 +206,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   __shared__ unsigned int work_s;
   __shared__ int gave_up;  // set by a wait that ran out: the waits after it return at once (see mbar_wait)
   __shared__ int first_pos_s;
+  __shared__ int split_order_s;  // of a split item: how many of its parts were through before this one
   constexpr int PAGE_STAGE = 256;
   __shared__ int box_pages[PAGE_STAGE];
 
@@ -211,9 +253,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // longest item.  With `parts` > 1 every item is `parts` draws that follow each other in the
   // hand-out: an item of many key tiles is worked on in up to `parts` stretches of at least
   // SPLIT_MIN_TILES tiles (the draws beyond that do nothing).  Every part of such an item
-  // leaves its unnormalised O, its reference maximum and its row sums in `split_scratch`, and
-  // `split_flags[item]` says how many parts there are (0: the item wrote its output itself);
-  // attention_prefill_merge_kernel, launched behind this one, adds the partials up.
+  // leaves its unnormalised O, its reference maximum and its row sums in `split_scratch`,
+  // and counts itself in `split_flags` (two ints an item: the parts that are through, zero
+  // between launches, and the number of parts of the item in the last launch that split, for
+  // tests to read); the part that counts last adds the partials up.
   const unsigned int n_subs = (group + heads_per_block - 1) / heads_per_block;
   const HandOut ho = hand_out(real_tiles, n_tiles_total, n_kv_heads, n_subs, parts, gridDim.x, split_slots, SPLIT);
   const int n_real = ho.n_real;
@@ -232,7 +275,6 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int b = tile_req[tile];
     const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     int n_tiles = 0;
-    if (SPLIT && parts > 1 && part == 0 && tid == 0 && b < 0) split_flags[item] = 0;  // a padding tile: nothing to merge
 
     // (uniform over the block; after a wait ran out the block only draws its items, so that
     // the counter still returns to zero)
@@ -278,7 +320,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
       n_tiles = SPLIT ? max(0, min(tiles_per_part, item_tiles - first_tile)) : item_tiles;
       const bool split = SPLIT && n_parts > 1;
       const int k_lo = k_begin / KEYS * KEYS + first_tile * KEYS;
-      if (SPLIT && parts > 1 && part == 0 && tid == 0) split_flags[item] = split ? n_parts : 0;
+      if (SPLIT && parts > 1 && part == 0 && tid == 0) split_flags[2 * item + 1] = split ? n_parts : 0;
       if (SPLIT && n_tiles > 0) stage_queries();  // (uniform over the block)
 
       if (n_tiles == 0) {
@@ -547,8 +589,21 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
           }
         } else {
           constexpr size_t SLOT = (size_t)ROWS * (HD + 2);
-          write_partial<HD>(tmem + my_lane + COL_O, split_scratch + ((size_t)item * parts + part) * SLOT + tid,
+          float* slots = split_scratch + (size_t)item * parts * SLOT;
+          write_partial<HD>(tmem + my_lane + COL_O, slots + part * SLOT + tid,
                             m_ref == -INFINITY ? -INFINITY : m_ref * c, l_run);
+          // Every part counts itself when its partial is complete; the one that counts last adds
+          // them all up (its own too, from where it left it: the sum does not depend on which
+          // part that is).  Nobody waits for anybody.
+          __threadfence();
+          asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_THREADS) : "memory");
+          if (tid == 0) split_order_s = atomicAdd(&split_flags[2 * item], 1);
+          asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_THREADS) : "memory");
+          if (split_order_s == n_parts - 1) {
+            __threadfence();
+            merge_parts<HD>(slots + tid, n_parts, dst, my_valid);
+            if (tid == 0) split_flags[2 * item] = 0;  // zero again for the next launch
+          }
         }
         tc_fence_before();
       }
@@ -576,65 +631,6 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap k_map, const __
   tc_fence_before();
   __syncthreads();
   if (warp == LOAD_WARP) tmem_dealloc(tmem, TMEM_COLS);
-}
-
-// Adds up the parts of the items that attention_prefill_tc5_kernel worked on in parts:
-// block (x, item) takes MERGE_THREADS of the item's ROWS * HD / 8 (row, 8 columns) pieces,
-// rows running fastest, so that a warp reads neighbouring floats of a partial.  The parts are
-// weighed by their reference maxima and summed in their order.
-constexpr int MERGE_THREADS = 256;
-
-template <int HD>
-__global__ void __launch_bounds__(MERGE_THREADS)
-attention_prefill_merge_kernel(const float* split_scratch, const int* split_flags, int parts, __nv_bfloat16* out,
-                               int out_stride, const int* tile_tok0, const int* tile_ntok, int n_tiles_total,
-                               int n_kv_heads, int group, int heads_per_block, int main_grid, int split_slots,
-                               const int* real_tiles) {
-  pdl_wait();
-  const unsigned int item = blockIdx.y;
-  const int n_subs = (group + heads_per_block - 1) / heads_per_block;
-  const HandOut ho = hand_out(real_tiles, n_tiles_total, n_kv_heads, n_subs, parts, main_grid, split_slots, true);
-  const int n_real = ho.n_real;
-  parts = ho.parts;
-  if (parts <= 1 || item >= (unsigned int)(n_real * n_kv_heads * n_subs)) return;
-  const int n_parts = (int)ld_global_4(split_flags + item);
-  if (n_parts <= 1) return;
-  const int piece = blockIdx.x * MERGE_THREADS + threadIdx.x;
-  const int row = piece % ROWS, col0 = piece / ROWS * 8;
-  if (col0 >= HD) return;
-  const int g = item % n_kv_heads;
-  const int tile = n_tiles_total - 1 - (int)((item / n_kv_heads) % n_real);
-  const int sub = item / n_kv_heads / n_real;
-  const int token = row / heads_per_block, head = sub * heads_per_block + row % heads_per_block;
-  if (token >= tile_ntok[tile] || head >= group) return;
-  constexpr size_t SLOT = (size_t)ROWS * (HD + 2);
-  const float* slots = split_scratch + (size_t)item * parts * SLOT;
-  float m_all = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) m_all = fmaxf(m_all, __ldcg(slots + p * SLOT + (size_t)HD * ROWS + row));
-  // the weight of part p (a part that saw no key has -inf and weighs nothing)
-  auto weight = [&](int p) {
-    const float m_p = __ldcg(slots + p * SLOT + (size_t)HD * ROWS + row);
-    return m_p == -INFINITY ? 0.f : exp2f(m_p - m_all);
-  };
-  float l_all = 0.f;
-  for (int p = 0; p < n_parts; ++p) l_all += __ldcg(slots + p * SLOT + (size_t)(HD + 1) * ROWS + row) * weight(p);
-  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll 4
-  for (int p = 0; p < n_parts; ++p) {
-    const float w = weight(p) * inv;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += __ldcg(slots + p * SLOT + (size_t)(col0 + i) * ROWS + row) * w;
-  }
-  uint4 v;
-  v.x = pack_bf16(acc[0], acc[1]);
-  v.y = pack_bf16(acc[2], acc[3]);
-  v.z = pack_bf16(acc[4], acc[5]);
-  v.w = pack_bf16(acc[6], acc[7]);
-  __nv_bfloat16* dst = out + (size_t)(tile_tok0[tile] + token) * out_stride + (g * group + head) * HD + col0;
-  *reinterpret_cast<uint4*>(dst) = v;
 }
 
 }  // namespace fg_tc5

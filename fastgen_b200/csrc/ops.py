@@ -413,7 +413,7 @@ class Ops:
                 self._split_retired.append((scratch, flags))
             room = max(items, 2 * room)
             scratch = torch.empty(room * PREFILL_TMA_ROWS * (head_dim + 2), dtype=torch.float32, device=self.device)
-            flags = torch.zeros(room, dtype=torch.int32, device=self.device)
+            flags = torch.zeros(2 * room, dtype=torch.int32, device=self.device)
             self._split[head_dim] = (scratch, flags, room)
         return scratch, flags, room
 
@@ -458,8 +458,6 @@ class Ops:
                 _check(lib, lib.fg_attention_prefill_tc5_bf16(
                     *args, _ptr(self._work_counter), _ptr(scratch), _ptr(flags), room, max_keys,
                     _ptr(tiles.count), nominal, _ptr(self.status), _stream()))
-                if 0 < want <= room:
-                    Ops.launches += 1  # the kernel that adds up the parts of split items
             else:
                 _check(lib, lib.fg_attention_prefill_tma_bf16(*args, _ptr(self.status), _stream()))
         elif tiles.n:

@@ -665,7 +665,7 @@ def test_long_prompt_in_large_portions(tmp_path, dtype, step_graphs):
     if dtype == torch.bfloat16:
         # the small portions' long items were worked on in parts (the prompt kernel leaves the
         # number of parts of every item of a launch that split), from captured graphs too
-        assert int(engine.ops._split[64][1].max()) >= 2
+        assert int(engine.ops._split[64][1][1::2].max()) >= 2
     got = H.collect(steps, outputs)["a"]
     ref = H.plain_logits(model_dir, toks)
     assert len(got) == 3 * 6 - 1 + 6  # (the portion of two tokens has two places)
