@@ -15,7 +15,6 @@ import bisect
 import gc
 from typing import Dict, List, Optional, Sequence
 
-import numpy as np
 import torch
 
 from ..csrc.ops import Ops
