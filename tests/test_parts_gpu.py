@@ -673,6 +673,51 @@ def test_long_prompt_in_large_portions(tmp_path, dtype, step_graphs):
         H.check_row(row, ref[p], dtype, f"pos {p}")
 
 
+@pytest.mark.parametrize("step_graphs", [False, True])
+def test_mixed_portions_on_long_contexts(tmp_path, step_graphs):
+    """Steps that mix portions of a few tokens of two requests with thousands of cached keys,
+    a fresh prompt and single tokens of two more requests: few attention items of very
+    different lengths in one launch (some worked on in parts, some not), eagerly and from
+    captured graphs whose tile lists have padding entries in front of the real ones."""
+    cfg = dict(
+        architectures=["LlamaForCausalLM"], hidden_size=256, intermediate_size=344, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, vocab_size=300, tie_word_embeddings=False,
+        rope_theta=500000.0, max_position_embeddings=8192,
+    )
+    from fastgen_b200.weights import write_random_model
+    model_dir = write_random_model(tmp_path / "mixed_long", cfg, seed=5, norm_jitter=0.1)
+    reqs = {"a": H.random_tokens(300, 3100, 1), "b": H.random_tokens(300, 1600, 2), "c": H.random_tokens(300, 90, 3),
+            "d": H.random_tokens(300, 2210, 4), "e": H.random_tokens(300, 530, 5)}
+    steps = []
+
+    def step(entries, end=()):
+        steps.append(dict(step=len(steps), entries=[dict(id=i, tokens=t, want=w) for i, t, w in entries], end=list(end)))
+
+    # most of a, b, d and e, each alone
+    step([("a", reqs["a"][:3000], [2999])])
+    step([("b", reqs["b"][:1500], [1499])])
+    step([("d", reqs["d"][:2200], [2199])])
+    step([("e", reqs["e"][:520], [519])])
+    # portions of a and b on their long contexts beside c's whole prompt and single tokens of d and e
+    step([("a", reqs["a"][3000:3040], [0, 39]), ("d", reqs["d"][2200:2201], [0]), ("b", reqs["b"][1500:1509], [8]),
+          ("c", reqs["c"][:70], [69]), ("e", reqs["e"][520:521], [0])])
+    step([("e", reqs["e"][521:522], [0]), ("a", reqs["a"][3040:3042], [0, 1]), ("b", reqs["b"][1509:1600], [0, 90]),
+          ("d", reqs["d"][2201:2202], [0]), ("c", reqs["c"][70:90], [19])], end=["b", "c"])
+    step([("a", reqs["a"][3042:3100], [57]), ("d", reqs["d"][2202:2203], [0]), ("e", reqs["e"][522:530], [7])],
+         end=["a", "d", "e"])
+    outputs, engine = H.run_engine(model_dir, torch.bfloat16, steps, page_size=64, max_tokens=8192, max_requests=5,
+                                   max_step_tokens=3072 if step_graphs else None)
+    if step_graphs:
+        assert engine.step_graphs is not None and engine.step_graphs.replays >= 6  # (the 520-token prompt is too far from its bucket and runs eagerly)
+    assert int(engine.ops._split[64][1][1::2].max()) >= 2  # some items were worked on in parts
+    got = H.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        ref = H.plain_logits(model_dir, toks)
+        assert got[rid], rid
+        for p, row in got[rid].items():
+            H.check_row(row, ref[p], torch.bfloat16, f"{rid} pos {p}")
+
+
 def test_many_key_splits_through_graphs(tmp_path):
     """Four live requests with thousands of cached keys and eight key/value heads: enough
     (request, head, split) items for the persistent single-token kernel, inside captured
