@@ -106,7 +106,8 @@ def test_linear_bf16(ops16):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("n,k", [(320, 192), (331, 200), (4096, 4096), (1000, 14336), (17, 72), (64, 8),
-                                 (20011, 136), (16000, 520)])  # the last two: many more row blocks than the GPU holds blocks
+                                 (20011, 136), (16000, 520),   # these two: many more row blocks than the GPU holds blocks
+                                 (6144, 4096), (5120, 3072), (5000, 72)])  # a little more than two blocks an SM: the shallow ring
 def test_gemm_skinny(ops16, request, m, n, k):
     g = torch.Generator().manual_seed(m + n + k)
     x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
@@ -161,7 +162,8 @@ def test_gemm_skinny_swiglu(ops16, m, f, k):
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 20])
-@pytest.mark.parametrize("hq,hkv,hd,page,dim", [(4, 1, 16, 8, 64), (6, 3, 32, 16, 192), (6, 2, 48, 8, 200), (32, 8, 128, 64, 4096)])
+@pytest.mark.parametrize("hq,hkv,hd,page,dim", [(4, 1, 16, 8, 64), (6, 3, 32, 16, 192), (6, 2, 48, 8, 200), (32, 8, 128, 64, 4096),
+                                                (24, 8, 128, 64, 3072)])
 def test_gemm_skinny_qkv_rope_write(ops16, m, hq, hkv, hd, page, dim):
     """Projection + rotation + page write in one kernel, against the three separate kernels."""
     from fastgen_b200.cache import LayerMemory
