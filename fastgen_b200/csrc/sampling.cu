@@ -84,7 +84,22 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   const int tid = threadIdx.x;
 
   ArgMax am = {-INFINITY, 0x7fffffff};
-  for (int i = tid; i < vocab; i += THREADS) am = better(am, ArgMax{x[i], i});
+  if ((((uintptr_t)x) & 15) == 0) {
+    // four logits a load (the row is a stream of a few hundred kilobytes that one block reads)
+    const int n4 = vocab >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+#pragma unroll 4
+    for (int i = tid; i < n4; i += THREADS) {
+      const float4 v = x4[i];
+      am = better(am, ArgMax{v.x, 4 * i});
+      am = better(am, ArgMax{v.y, 4 * i + 1});
+      am = better(am, ArgMax{v.z, 4 * i + 2});
+      am = better(am, ArgMax{v.w, 4 * i + 3});
+    }
+    for (int i = 4 * n4 + tid; i < vocab; i += THREADS) am = better(am, ArgMax{x[i], i});
+  } else {
+    for (int i = tid; i < vocab; i += THREADS) am = better(am, ArgMax{x[i], i});
+  }
   am = block_argmax(am, as);
   const float xmax = am.v;
   const float temp = temps ? temps[row] : 0.f;
