@@ -78,27 +78,40 @@ __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uin
 }
 
 // 16-byte pieces a thread copies per chunk (4 of W, the rest of x), ring depth, ring size.
-// SHALLOW (up to 8 tokens only): three stages instead of four, 72 KiB a block, so that three
-// blocks share an SM (the warps' sums then go to the ring's memory once it is through, not to
-// memory of their own).  A launch of a little more than two blocks an SM runs as one and a
-// fraction of a second round, and the fraction costs about as much as a whole one (measured:
-// 296 blocks of 16 rows of 4,096 in 7.8 us, 320 in 10.7, 384 in 12.9, 592 in 14.7); with three
-// blocks an SM up to 444 blocks run at once, with as many bytes in flight an SM.
-template <int NT, bool SHALLOW = false>
+// How many blocks share an SM is chosen with the ring (up to 8 tokens; the warps' sums then go
+// to the ring's memory once it is through, not to memory of their own):
+//  * TWO_AN_SM: four stages, 96 KiB a block.  The shared-memory carve-out is asked to be no
+//    larger than the two blocks need (196 KiB), which leaves the L1 room for x: every block reads
+//    all of x, 64 KiB at 8 tokens of 4,096, and a product of 28,672 rows took 40.5 us with the
+//    largest carve-out against 38.7 (36.7 with one token).
+//  * THREE_AN_SM: three stages, 72 KiB.  A launch of a little more than two blocks an SM runs
+//    as one round and a fraction of a second one, and the fraction costs about as much as a
+//    whole round (16 rows of 4,096 a block, 8 tokens: 296 blocks 7.8 us, 320 blocks 10.7, 384
+//    blocks 12.9, 592 blocks 14.7); with three blocks an SM up to 444 blocks run at once, with
+//    as many bytes in flight an SM (320 blocks 9.0 us, 384 blocks 9.7).
+//  * ONE_AN_SM: six stages, 144 KiB.  A launch of no more blocks than SMs is otherwise placed
+//    two blocks an SM on half of the SMs.
+enum { TWO_AN_SM = 0, THREE_AN_SM = 1, ONE_AN_SM = 2 };
+
+template <int NT, int MODE = TWO_AN_SM>
 struct Ring {
-  static_assert(!SHALLOW || NT == 1, "the shallow ring is for up to 8 tokens");
+  static_assert(MODE == TWO_AN_SM || NT == 1, "the other rings are for up to 8 tokens");
   static constexpr int PIECES = 4 + 2 * NT;
-  static constexpr int STAGES = SHALLOW ? 3 : (NT == 1 ? 4 : (NT == 2 ? 3 : 2));  // 96 KiB a block: two blocks an SM
+  static constexpr int STAGES =
+      MODE == THREE_AN_SM ? 3 : (MODE == ONE_AN_SM ? 6 : (NT == 1 ? 4 : (NT == 2 ? 3 : 2)));  // 96 KiB: two blocks an SM
   static constexpr size_t BYTES = (size_t)STAGES * PIECES * THREADS * 16;
+  static constexpr bool SUMS_IN_RING = NT == 1;
+  // per cent of the largest carve-out to ask for (0: the driver's choice)
+  static constexpr int CARVEOUT = NT != 1 ? 0 : (MODE == THREE_AN_SM ? 100 : (MODE == ONE_AN_SM ? 70 : 80));
 };
 
 // One block's product: 16 rows of W (from row n0) against the tokens' x.  The pieces a
 // thread streams, its ring and its accumulators; the callers decide when the weights'
 // first stages are issued (they may go ahead of data that is not ready yet).
-template <int NT, bool SHALLOW = false>
+template <int NT, int MODE = TWO_AN_SM>
 struct BlockProduct {
-  static constexpr int PIECES = Ring<NT, SHALLOW>::PIECES;
-  static constexpr int STAGES = Ring<NT, SHALLOW>::STAGES;
+  static constexpr int PIECES = Ring<NT, MODE>::PIECES;
+  static constexpr int STAGES = Ring<NT, MODE>::STAGES;
   uint4* ring;  // [STAGES][PIECES][THREADS]
   const __nv_bfloat16 *wa, *wb, *xr[NT];
   bool row_a, row_b, tok_ok[NT];
@@ -181,7 +194,7 @@ struct BlockProduct {
         }
       }
     }
-    if (SHALLOW) __syncthreads();  // `red` is the ring's memory: every thread is through with its stages
+    if (Ring<NT, MODE>::SUMS_IN_RING) __syncthreads();  // `red` is the ring's memory: every thread is through with its stages
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       red[warp][r][nt * 8 + 2 * c] = acc[nt][0];
@@ -224,16 +237,17 @@ __device__ __forceinline__ void epilogue_swiglu(float (*red)[ROWS][NT * 8], TO* 
   }
 }
 
-template <int NT, typename TO, int EPI, bool SHALLOW = false>
+template <int NT, typename TO, int EPI, int MODE = TWO_AN_SM>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restrict__ w, int ldw,
                    TO* __restrict__ y, int ldy, int M, int N, int K, QkvEpilogue qkv) {
   extern __shared__ __align__(16) unsigned char ring_raw[];
-  __shared__ float red_own[SHALLOW ? 1 : WARPS][ROWS][NT * 8];
-  float (*red)[ROWS][NT * 8] = SHALLOW ? reinterpret_cast<float (*)[ROWS][NT * 8]>(ring_raw) : red_own;
+  constexpr bool RED_IN_RING = Ring<NT, MODE>::SUMS_IN_RING;
+  __shared__ float red_own[RED_IN_RING ? 1 : WARPS][ROWS][NT * 8];
+  float (*red)[ROWS][NT * 8] = RED_IN_RING ? reinterpret_cast<float (*)[ROWS][NT * 8]>(ring_raw) : red_own;
   const int tid = threadIdx.x;
   const int n0 = blockIdx.x * ROWS;
-  BlockProduct<NT, SHALLOW> block;
+  BlockProduct<NT, MODE> block;
   block.setup(reinterpret_cast<uint4*>(ring_raw), x, ldx, w, ldw, M, N, K, n0);
 
   // The weights do not depend on the kernel before this one: their first stages are on
@@ -300,15 +314,19 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* __restr
   }
 }
 
-template <int NT, typename TO, int EPI, bool SHALLOW = false>
+template <int NT, typename TO, int EPI, int MODE = TWO_AN_SM>
 int launch_one(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
                const QkvEpilogue& qkv, cudaStream_t stream) {
-  auto kern = gemm_skinny_kernel<NT, TO, EPI, SHALLOW>;
-  constexpr size_t smem = Ring<NT, SHALLOW>::BYTES;
+  auto kern = gemm_skinny_kernel<NT, TO, EPI, MODE>;
+  constexpr size_t smem = Ring<NT, MODE>::BYTES;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FG_CHECK_ARG(e == cudaSuccess, "fg_gemm_skinny: shared memory: %s", cudaGetErrorString(e));
+    if (Ring<NT, MODE>::CARVEOUT) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, Ring<NT, MODE>::CARVEOUT);
+      FG_CHECK_ARG(e == cudaSuccess, "fg_gemm_skinny: carve-out: %s", cudaGetErrorString(e));
+    }
     attr_set = true;
   }
   fg_launch_pdl(kern, dim3((N + ROWS - 1) / ROWS), dim3(THREADS), smem, stream, (const __nv_bfloat16*)x, ldx,
@@ -320,7 +338,7 @@ template <typename TO, int EPI>
 int launch(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int M, int N, int K,
            const QkvEpilogue& qkv, cudaStream_t stream) {
   if (M <= 8) {
-    // a little more than two blocks an SM: three an SM run them all at once (see Ring)
+    // how many blocks share an SM goes by the number of blocks (see Ring)
     static int n_sms = 0;
     if (n_sms == 0) {
       int dev = 0;
@@ -329,7 +347,8 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* y, int ldy, int
     }
     const int blocks = (N + ROWS - 1) / ROWS;
     if (blocks > 2 * n_sms && blocks <= 3 * n_sms)
-      return launch_one<1, TO, EPI, true>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+      return launch_one<1, TO, EPI, THREE_AN_SM>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
+    if (blocks <= n_sms) return launch_one<1, TO, EPI, ONE_AN_SM>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
     return launch_one<1, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
   }
   if (M <= 16) return launch_one<2, TO, EPI>(x, ldx, w, ldw, y, ldy, M, N, K, qkv, stream);
